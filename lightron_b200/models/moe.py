@@ -1,0 +1,59 @@
+"""Sparse mixture-of-experts feed-forward with expert parallelism.
+
+Parity: ``MoEFeedForward`` in the reference's ``model/model.py:72-116``: a bias-free ``gate`` linear,
+softmax over experts then top-k (``:96-98``), dispatch, expert SwiGLU MLPs, combine and a sum over
+the k slots weighted by the (un-renormalised) router probabilities (``:115``).  Completed here:
+each rank allocates only its own experts (the reference allocates all of them on every rank,
+``:88``), every local expert is applied to its own tokens (``:109`` applies expert 0 to all) and a
+Switch-style load-balance auxiliary loss ``E * sum_e f_e * P_e`` is produced.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..config import ModelArgs
+from ..ops import functional as OF
+from ..parallel.ep import ExpertParallel
+from ..parallel.tp import Linear
+
+
+class MoEFeedForward(nn.Module):
+    def __init__(self, args: ModelArgs, ctx, **kw):
+        super().__init__()
+        from .llama import MLP
+        self.num_experts = args.moe_num_experts
+        self.topk = args.moe_topk
+        self.gate = Linear(args.dim, self.num_experts, **kw)
+        group = ctx.ep_group if args.ep_size > 1 else None
+        self.ep = ExpertParallel(self.num_experts, group)
+        lo = self.ep.first_expert
+        self.experts = nn.ModuleDict({str(e): MLP(args, ctx, **kw) for e in range(lo, lo + self.ep.local_experts)})
+        for p in self.experts.parameters():
+            p.is_expert = True
+        self.sp = args.sequence_parallel and args.tp_size > 1
+        self.tp_group = ctx.tp_group if args.tp_size > 1 else None
+        self.last_aux_loss = None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """x [T, H] -> [T, H]."""
+        from ..parallel import comm
+        if self.sp:                       # experts see whole tokens; gather the row shards first
+            x = comm.gather_rows_replicated(x, self.tp_group)
+        T, H = x.shape
+        logits = OF.linear(x, self.gate.weight).float()
+        probs = F.softmax(logits, dim=-1)
+        weights, indices = torch.topk(probs, self.topk, dim=-1)
+        # load-balance loss: fraction of routed copies per expert x mean router probability
+        with torch.no_grad():
+            frac = torch.bincount(indices.reshape(-1), minlength=self.num_experts).float() / (T * self.topk)
+        self.last_aux_loss = self.num_experts * torch.sum(frac * probs.mean(dim=0))
+        tokens, meta = self.ep.dispatch(x, indices)
+        experts = [lambda t, m=m: m(t, sp=False) for m in self.experts.values()]
+        y = self.ep.apply_experts(tokens, meta, experts)
+        y = self.ep.combine(y, meta)                             # [T, k, H]
+        out = (y.float() * weights.unsqueeze(-1)).sum(dim=1).to(x.dtype)
+        if self.sp:
+            out = comm.split_rows(out, self.tp_group)
+        return out

@@ -1,0 +1,513 @@
+"""Differentiable ops.  CUDA bf16 tensors run the hand-written sm_100a kernels; every other
+tensor runs the PyTorch oracle in ``ops.reference`` (CPU ranks, fp32 parity runs).
+
+Call sites these replace in the reference: ``F.linear`` (parallel/parallel_tp.py:69,100;
+model/model.py:155,202), ``RMSNorm`` (layers/layers.py:5-16), ``apply_rotary_emb``
+(layers/layers.py:44-70), ``F.silu(w1 x) * w3 x`` (model/model.py:69),
+``F.scaled_dot_product_attention`` (model/model.py:193-198), ``F.embedding`` (model/model.py:261)
+and ``F.cross_entropy`` (trainer.py:52).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import native, reference as ref
+
+# --------------------------------------------------------------------------------------
+# GEMM
+# --------------------------------------------------------------------------------------
+
+
+def _rows_adjacent(ws: Sequence[torch.Tensor]) -> bool:
+    """True when the [n_i, K] matrices sit back to back in memory (one [sum n_i, K] matrix)."""
+    for a, b in zip(ws[:-1], ws[1:]):
+        if not (a.is_contiguous() and b.is_contiguous()):
+            return False
+        if a.data_ptr() + a.numel() * a.element_size() != b.data_ptr():
+            return False
+    return True
+
+
+def _as_strided_cat(ws: Sequence[torch.Tensor]) -> torch.Tensor:
+    """View adjacent [n_i, K] matrices as one [sum n_i, K] matrix without copying."""
+    n = sum(w.shape[0] for w in ws)
+    return ws[0].as_strided((n, ws[0].shape[1]), (ws[0].shape[1], 1))
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = False,
+         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C[M,N] = A . B^T on the tcgen05 kernel.  ``a_mn``: A is stored [K, M] (M contiguous)
+    instead of [M, K]; ``b_mn``: B is stored [K, N] instead of [N, K].  Row strides are free
+    (multiples of 8 elements), inner stride must be 1."""
+    assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+    M, K = (a.shape[1], a.shape[0]) if a_mn else a.shape
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else b.shape
+    assert K == Kb, f"K mismatch {K} vs {Kb}"
+    if out is None:
+        out = torch.empty(M, N, dtype=a.dtype, device=a.device)
+    native.call("lb_gemm_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K,
+                a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn), 0, native.stream_ptr())
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    """y = x W^T for one weight or several row-adjacent weights (fused QKV / gate+up)."""
+
+    @staticmethod
+    def forward(ctx, x, *ws):
+        x2 = x.reshape(-1, x.shape[-1])
+        ctx.fused = _rows_adjacent(ws)
+        ctx.save_for_backward(x2, *ws)
+        ctx.xshape = x.shape
+        if ctx.fused:
+            y = gemm(x2, _as_strided_cat(ws))
+        else:
+            y = torch.cat([gemm(x2, w) for w in ws], dim=1)
+        return y.view(*x.shape[:-1], y.shape[-1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, *ws = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        sizes = [w.shape[0] for w in ws]
+        dx = None
+        if ctx.needs_input_grad[0]:
+            if ctx.fused:
+                dx = gemm(dy2, _as_strided_cat(ws), b_mn=True)
+            else:
+                off = 0
+                for w, n in zip(ws, sizes):
+                    part = gemm(dy2[:, off:off + n], w, b_mn=True)
+                    dx = part if dx is None else dx.add_(part)
+                    off += n
+            dx = dx.view(ctx.xshape)
+        dws: List[Optional[torch.Tensor]] = [None] * len(ws)
+        if any(ctx.needs_input_grad[1:]):
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True)        # [sum n_i, K]
+            off = 0
+            for i, n in enumerate(sizes):
+                dws[i] = dw[off:off + n]
+                off += n
+        return (dx, *dws)
+
+
+def linear(x: torch.Tensor, *ws: torch.Tensor) -> torch.Tensor:
+    """x [..., K] times one or more [n_i, K] weights -> [..., sum n_i]."""
+    if native.use_native(x):
+        return _Linear.apply(x, *ws)
+    if len(ws) == 1:
+        return F.linear(x, ws[0])
+    return torch.cat([F.linear(x, w) for w in ws], dim=-1)
+
+
+# --------------------------------------------------------------------------------------
+# RMSNorm (optionally fused with the residual add that precedes it)
+# --------------------------------------------------------------------------------------
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, res, w, eps):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        rows, cols = x2.shape
+        y = torch.empty_like(x2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        if res is not None:
+            r2 = res.reshape(-1, shape[-1])
+            if not r2.is_contiguous():
+                r2 = r2.contiguous()
+            h = torch.empty_like(x2)
+        else:
+            r2, h = None, None
+        native.call("lb_rmsnorm_fwd", x2.data_ptr(), native.ptr(r2), w.data_ptr(), native.ptr(h), y.data_ptr(),
+                    rstd.data_ptr(), rows, cols, float(eps), native.stream_ptr())
+        src = h if res is not None else x2
+        ctx.save_for_backward(src, w, rstd)
+        ctx.has_res = res is not None
+        ctx.shape = shape
+        if res is not None:
+            return h.view(shape), y.view(shape)
+        return y.view(shape)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        src, w, rstd = ctx.saved_tensors
+        rows, cols = src.shape
+        if ctx.has_res:
+            dh, dy = grads
+        else:
+            dh, dy = None, grads[0]
+        dy2 = dy.reshape(rows, cols)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dh2 = None
+        if dh is not None:
+            dh2 = dh.reshape(rows, cols)
+            if not dh2.is_contiguous():
+                dh2 = dh2.contiguous()
+        lib = native.require()
+        nblk = lib.lb_rmsnorm_bwd_blocks(rows, cols)
+        partial = torch.empty(nblk, cols, dtype=torch.float32, device=src.device)
+        dx = torch.empty_like(src)
+        dw = torch.empty_like(w)
+        native.call("lb_rmsnorm_bwd", dy2.data_ptr(), src.data_ptr(), w.data_ptr(), rstd.data_ptr(), native.ptr(dh2),
+                    dx.data_ptr(), partial.data_ptr(), dw.data_ptr(), rows, cols, nblk, native.stream_ptr())
+        dxv = dx.view(ctx.shape)
+        if ctx.has_res:
+            return dxv, dxv, dw, None
+        return dxv, None, dw, None
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    if native.use_native(x):
+        return _RMSNorm.apply(x, None, w, eps)
+    return ref.rmsnorm(x, w, eps)
+
+
+def add_rmsnorm(x: torch.Tensor, res: torch.Tensor, w: torch.Tensor, eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    """h = x + res; y = rmsnorm(h).  Returns (h, y) from one pass over memory."""
+    if native.use_native(x):
+        return _RMSNorm.apply(x, res, w, eps)
+    h = x + res
+    return h, ref.rmsnorm(h, w, eps)
+
+
+# --------------------------------------------------------------------------------------
+# RoPE
+# --------------------------------------------------------------------------------------
+
+
+def _rope_native_(t: torch.Tensor, cos, sin, positions, S: int, n_heads: int, head_dim: int, inverse: bool) -> None:
+    """In place on a [T, *] row-major view whose first n_heads*head_dim columns are heads."""
+    T = t.shape[0]
+    native.call("lb_rope", t.data_ptr(), cos.data_ptr(), sin.data_ptr(), native.ptr(positions), T, S, n_heads,
+                head_dim, t.stride(0), int(inverse), native.stream_ptr())
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin, positions):
+        B, S, h, d = x.shape
+        out = x.contiguous().clone()
+        _rope_native_(out.view(B * S, h * d), cos, sin, positions, S, h, d, False)
+        ctx.save_for_backward(cos, sin, positions)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin, positions = ctx.saved_tensors
+        B, S, h, d = dy.shape
+        dx = dy.contiguous().clone()
+        _rope_native_(dx.view(B * S, h * d), cos, sin, positions, S, h, d, True)
+        return dx, None, None, None
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, positions: Optional[torch.Tensor] = None):
+    """x [B, S, h, d] -> rotated copy.  ``positions`` [S] int32 picks table rows."""
+    if native.use_native(x):
+        if positions is not None and positions.dtype != torch.int32:
+            positions = positions.to(torch.int32)
+        return _Rope.apply(x, cos, sin, positions)
+    return ref.rope(x, cos, sin, positions)
+
+
+# --------------------------------------------------------------------------------------
+# SwiGLU on a fused [T, 2I] gate|up tensor
+# --------------------------------------------------------------------------------------
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        shape = gu.shape
+        gu2 = gu.reshape(-1, shape[-1])
+        I = shape[-1] // 2
+        out = torch.empty(gu2.shape[0], I, dtype=gu.dtype, device=gu.device)
+        native.call("lb_swiglu_fwd", gu2.data_ptr(), out.data_ptr(), gu2.shape[0], I, gu2.stride(0), native.stream_ptr())
+        ctx.save_for_backward(gu2)
+        ctx.shape = shape
+        return out.view(*shape[:-1], I)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (gu2,) = ctx.saved_tensors
+        I = gu2.shape[1] // 2
+        dy2 = dy.reshape(-1, I)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dgu = torch.empty(gu2.shape[0], 2 * I, dtype=gu2.dtype, device=gu2.device)
+        native.call("lb_swiglu_bwd", gu2.data_ptr(), dy2.data_ptr(), dgu.data_ptr(), gu2.shape[0], I, gu2.stride(0),
+                    native.stream_ptr())
+        return dgu.view(ctx.shape)
+
+
+def swiglu(gu: torch.Tensor) -> torch.Tensor:
+    """gu [..., 2I] holding gate | up -> silu(gate) * up [..., I]."""
+    if native.use_native(gu):
+        return _SwiGLU.apply(gu)
+    I = gu.shape[-1] // 2
+    return ref.swiglu(gu[..., :I], gu[..., I:])
+
+
+# --------------------------------------------------------------------------------------
+# Attention
+# --------------------------------------------------------------------------------------
+
+
+def _layout_ok(t: torch.Tensor) -> bool:
+    B, S, h, d = t.shape
+    return t.stride(3) == 1 and t.stride(2) == d and (B == 1 or t.stride(0) == S * t.stride(1)) \
+        and t.stride(1) % 8 == 0 and t.data_ptr() % 16 == 0
+
+
+def _check_attn_layout(t: torch.Tensor) -> None:
+    if not _layout_ok(t):
+        raise ValueError(f"attention operand must be [B,S,h,d] with unit inner stride, head stride d, batch "
+                         f"stride S*token_stride and 16-byte aligned rows; got shape {tuple(t.shape)} "
+                         f"strides {t.stride()}")
+
+
+def _fix_layout(t: torch.Tensor) -> torch.Tensor:
+    return t if _layout_ok(t) else t.contiguous()
+
+
+def flash_fwd_native(q, k, v, causal: bool, scale: float):
+    q, k, v = _fix_layout(q), _fix_layout(k), _fix_layout(v)
+    B, Sq, hq, d = q.shape
+    Sk, hkv = k.shape[1], k.shape[2]
+    o = torch.empty(B, Sq, hq, d, dtype=q.dtype, device=q.device)
+    lse = torch.empty(B, hq, Sq, dtype=torch.float32, device=q.device)
+    native.call("lb_flash_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                B, Sq, Sk, hq, hkv, d, q.stride(1), k.stride(1), v.stride(1), o.stride(1), float(scale), int(causal),
+                native.stream_ptr())
+    return o, lse
+
+
+def flash_bwd_native(q, k, v, o, lse, do, causal: bool, scale: float, dq=None, dk=None, dv=None):
+    """Returns (dq, dk, dv).  Output tensors may be caller-provided strided views."""
+    B, Sq, hq, d = q.shape
+    Sk, hkv = k.shape[1], k.shape[2]
+    if dq is None:
+        dq = torch.empty(B, Sq, hq, d, dtype=q.dtype, device=q.device)
+    if dk is None:
+        dk = torch.empty(B, Sk, hkv, d, dtype=q.dtype, device=q.device)
+    if dv is None:
+        dv = torch.empty(B, Sk, hkv, d, dtype=q.dtype, device=q.device)
+    q, k, v, o, do = (_fix_layout(t) for t in (q, k, v, o, do))
+    lse = lse.contiguous()
+    for t in (dq, dk, dv):
+        _check_attn_layout(t)
+    delta = torch.empty(B, hq, Sq, dtype=torch.float32, device=q.device)
+    dq_acc = torch.zeros(B, Sq, hq, d, dtype=torch.float32, device=q.device)
+    native.call("lb_flash_bwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                delta.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                B, Sq, Sk, hq, hkv, d, q.stride(1), k.stride(1), v.stride(1), o.stride(1), do.stride(1),
+                dq.stride(1), dk.stride(1), dv.stride(1), float(scale), int(causal), native.stream_ptr())
+    return dq, dk, dv
+
+
+class _FlashAttn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        o, lse = flash_fwd_native(q, k, v, causal, scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = flash_bwd_native(q, k, v, o, lse, do, ctx.causal, ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def flash_attention(q, k, v, causal: bool = True, scale: Optional[float] = None):
+    """q [B,Sq,hq,d], k/v [B,Sk,hkv,d] -> [B,Sq,hq,d]; GQA by indexing (no repeat_kv)."""
+    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+    if native.use_native(q):
+        return _FlashAttn.apply(q, k, v, causal, scale)
+    return ref.attention(q, k, v, causal=causal, scale=scale)
+
+
+class _RopeAttnQKV(torch.autograd.Function):
+    """RoPE + causal attention straight on the fused projection output [B*S, (hq+2hkv)*d].
+    Forward rotates q and k in place inside ``qkv`` without telling autograd: the producer is
+    a GEMM whose backward needs its inputs, not this output, and nothing else may consume the
+    tensor (the caller hands over ownership).  Backward writes one dqkv tensor and un-rotates
+    its q,k columns in place, so no slice/concat copies exist on either side."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, positions, B, S, hq, hkv, d, scale):
+        T = B * S
+        qkv2 = qkv.view(T, (hq + 2 * hkv) * d)
+        _rope_native_(qkv2, cos, sin, positions, S, hq + hkv, d, False)
+        row = qkv2.stride(0)
+        off = qkv2.storage_offset()
+        q = qkv2.as_strided((B, S, hq, d), (S * row, row, d, 1), off)
+        k = qkv2.as_strided((B, S, hkv, d), (S * row, row, d, 1), off + hq * d)
+        v = qkv2.as_strided((B, S, hkv, d), (S * row, row, d, 1), off + (hq + hkv) * d)
+        o, lse = flash_fwd_native(q, k, v, True, scale)
+        ctx.save_for_backward(qkv, o, lse, cos, sin, positions)
+        ctx.dims = (B, S, hq, hkv, d, scale)
+        return o.view(T, hq * d)
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, o, lse, cos, sin, positions = ctx.saved_tensors
+        B, S, hq, hkv, d, scale = ctx.dims
+        T = B * S
+        qkv2 = qkv.view(T, (hq + 2 * hkv) * d)
+        row = qkv2.stride(0)
+        off = qkv2.storage_offset()
+        q = qkv2.as_strided((B, S, hq, d), (S * row, row, d, 1), off)
+        k = qkv2.as_strided((B, S, hkv, d), (S * row, row, d, 1), off + hq * d)
+        v = qkv2.as_strided((B, S, hkv, d), (S * row, row, d, 1), off + (hq + hkv) * d)
+        dqkv = torch.empty(T, (hq + 2 * hkv) * d, dtype=qkv2.dtype, device=qkv2.device)
+        drow = dqkv.stride(0)
+        dq = dqkv.as_strided((B, S, hq, d), (S * drow, drow, d, 1), 0)
+        dk = dqkv.as_strided((B, S, hkv, d), (S * drow, drow, d, 1), hq * d)
+        dv = dqkv.as_strided((B, S, hkv, d), (S * drow, drow, d, 1), (hq + hkv) * d)
+        flash_bwd_native(q, k, v, o, lse, do.reshape(B, S, hq, d), True, scale, dq, dk, dv)
+        _rope_native_(dqkv, cos, sin, positions, S, hq + hkv, d, True)
+        return dqkv.view(qkv.shape), None, None, None, None, None, None, None, None, None
+
+
+def rope_attention_qkv(qkv: torch.Tensor, cos, sin, positions, B: int, S: int, hq: int, hkv: int, d: int,
+                       scale: Optional[float] = None) -> torch.Tensor:
+    """qkv [B*S, (hq+2hkv)*d] (q heads | k heads | v heads per token) -> attention output
+    [B*S, hq*d] with RoPE applied to q and k.  Causal, full sequence local."""
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    if native.use_native(qkv):
+        if positions is not None and positions.dtype != torch.int32:
+            positions = positions.to(torch.int32)
+        return _RopeAttnQKV.apply(qkv, cos, sin, positions, B, S, hq, hkv, d, scale)
+    T = B * S
+    q, k, v = qkv.view(T, -1).split([hq * d, hkv * d, hkv * d], dim=-1)
+    q = ref.rope(q.reshape(B, S, hq, d), cos, sin, positions)
+    k = ref.rope(k.reshape(B, S, hkv, d), cos, sin, positions)
+    o = ref.attention(q, k, v.reshape(B, S, hkv, d), causal=True, scale=scale)
+    return o.reshape(T, hq * d)
+
+
+# --------------------------------------------------------------------------------------
+# Embedding (optionally vocab-parallel)
+# --------------------------------------------------------------------------------------
+
+
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tokens, w, vocab_start):
+        T = tokens.numel()
+        H = w.shape[1]
+        out = torch.empty(T, H, dtype=w.dtype, device=w.device)
+        tok = tokens.reshape(-1).contiguous()
+        native.call("lb_embedding_fwd", tok.data_ptr(), w.data_ptr(), out.data_ptr(), T, H, vocab_start,
+                    vocab_start + w.shape[0], native.stream_ptr())
+        ctx.save_for_backward(tok)
+        ctx.wshape, ctx.vocab_start = w.shape, vocab_start
+        return out.view(*tokens.shape, H)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (tok,) = ctx.saved_tensors
+        V, H = ctx.wshape
+        dy2 = dy.reshape(-1, H)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dw = torch.zeros(V, H, dtype=dy.dtype, device=dy.device)
+        native.call("lb_embedding_bwd", tok.data_ptr(), dy2.data_ptr(), dw.data_ptr(), tok.numel(), H,
+                    ctx.vocab_start, ctx.vocab_start + V, native.stream_ptr())
+        return None, dw, None
+
+
+def embedding(tokens: torch.Tensor, w: torch.Tensor, vocab_start: int = 0) -> torch.Tensor:
+    """Rows of ``w`` (which holds vocab ids [vocab_start, vocab_start + w.shape[0])); ids outside
+    the range give zero rows (vocab-parallel partial result, parallel/parallel_tp.py:131-143)."""
+    if native.use_native(w):
+        return _Embedding.apply(tokens, w, vocab_start)
+    local = tokens - vocab_start
+    mask = (local < 0) | (local >= w.shape[0])
+    out = F.embedding(local.masked_fill(mask, 0), w)
+    if vocab_start != 0 or bool(mask.any()):
+        out = out.masked_fill(mask.unsqueeze(-1), 0.0)
+    return out
+
+
+# --------------------------------------------------------------------------------------
+# Cross-entropy, vocab-parallel aware: ranks exchange (max, sum-exp, target logit) per token,
+# never logits (the reference all-gathers [B,S,V] logits: parallel/parallel_tp.py:31,72).
+# --------------------------------------------------------------------------------------
+
+
+class _CrossEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets, vocab_start, group, n_valid_total, ignore_index):
+        T, V = logits.shape
+        use_native = native.use_native(logits)
+        tgt = targets.reshape(-1).contiguous()
+        if use_native:
+            mx = torch.empty(T, dtype=torch.float32, device=logits.device)
+            se = torch.empty(T, dtype=torch.float32, device=logits.device)
+            tl = torch.empty(T, dtype=torch.float32, device=logits.device)
+            native.call("lb_ce_stats", logits.data_ptr(), tgt.data_ptr(), mx.data_ptr(), se.data_ptr(), tl.data_ptr(),
+                        T, V, logits.stride(0), vocab_start, native.stream_ptr())
+        else:
+            lf = logits.float()
+            mx = lf.max(dim=-1).values
+            se = torch.exp(lf - mx[:, None]).sum(-1)
+            local = tgt - vocab_start
+            inr = (local >= 0) & (local < V)
+            tl = torch.where(inr, lf.gather(1, local.clamp(0, V - 1)[:, None])[:, 0], torch.zeros_like(mx))
+        if group is not None and dist.get_world_size(group) > 1:
+            gmx = mx.clone()
+            dist.all_reduce(gmx, op=dist.ReduceOp.MAX, group=group)
+            packed = torch.stack((se * torch.exp(mx - gmx), tl))
+            dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
+            se, tl, mx = packed[0], packed[1], gmx
+        lse = mx + torch.log(se)
+        valid = tgt != ignore_index
+        n_valid = n_valid_total if n_valid_total is not None else int(valid.sum().item())
+        per_tok = torch.where(valid, lse - tl, torch.zeros_like(lse))
+        loss = per_tok.sum() / max(n_valid, 1)
+        ctx.save_for_backward(logits, tgt, lse)
+        ctx.meta = (vocab_start, n_valid, ignore_index, use_native)
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        logits, tgt, lse = ctx.saved_tensors
+        vocab_start, n_valid, ignore_index, use_native = ctx.meta
+        T, V = logits.shape
+        if use_native:
+            # dlogits overwrites the logits buffer: it is dead after the loss, and at
+            # [16384, 32000] it is the largest activation of the step.
+            dl = dloss.float().reshape(1).contiguous()      # read on the device: no host sync
+            native.call("lb_ce_grad", logits.data_ptr(), tgt.data_ptr(), lse.data_ptr(), logits.data_ptr(),
+                        dl.data_ptr(), T, V, logits.stride(0), vocab_start, 1.0 / max(n_valid, 1), ignore_index,
+                        native.stream_ptr())
+            return logits, None, None, None, None, None
+        p = torch.exp(logits.float() - lse[:, None])
+        local = tgt - vocab_start
+        inr = (local >= 0) & (local < V)
+        idx = torch.nonzero(inr, as_tuple=False)[:, 0]
+        p[idx, local[idx]] -= 1.0
+        p = p * (tgt != ignore_index)[:, None]
+        return (p * (dloss.float() / max(n_valid, 1))).to(logits.dtype), None, None, None, None, None
+
+
+def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, vocab_start: int = 0, group=None,
+                  n_valid_total: Optional[int] = None, ignore_index: int = -100) -> torch.Tensor:
+    """Mean NLL of [T, V_local] logits.  With ``group`` the vocab dim is sharded across it.
+    ``n_valid_total`` (the number of non-ignored targets) avoids a host sync when known."""
+    logits2 = logits.reshape(-1, logits.shape[-1])
+    return _CrossEntropy.apply(logits2, targets, vocab_start, group, n_valid_total, ignore_index)

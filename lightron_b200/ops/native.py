@@ -1,0 +1,125 @@
+"""ctypes binding of the in-tree CUDA library (``lightron_b200/csrc/liblightron_b200.so``).
+
+The library is plain ``extern "C"``: every entry point takes raw device pointers, sizes and a
+``cudaStream_t`` and returns 0 or a negative error code, so it builds in seconds with nvcc alone
+and does not depend on the torch C++ ABI.  On a machine with a GPU a missing library is an error
+(``require()``), never a silent fallback to library kernels.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_int, c_int64, c_float, c_void_p
+from typing import Optional
+
+import torch
+
+_LIB: Optional[ctypes.CDLL] = None
+_LIB_ERR: Optional[str] = None
+LIB_NAME = "liblightron_b200.so"
+
+
+def lib_path() -> str:
+    return os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc", LIB_NAME)
+
+
+_P, _I, _L, _F = c_void_p, c_int, c_int64, c_float
+
+# name -> argtypes (all return int)
+_SIGNATURES = {
+    "lb_last_error": [],
+    "lb_device_status": [_P],
+    "lb_rmsnorm_fwd": [_P, _P, _P, _P, _P, _P, _I, _I, _F, _P],
+    "lb_rmsnorm_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "lb_rmsnorm_bwd_blocks": [_I, _I],
+    "lb_rope": [_P, _P, _P, _P, _I, _I, _I, _I, _L, _I, _P],
+    "lb_swiglu_fwd": [_P, _P, _I, _I, _L, _P],
+    "lb_swiglu_bwd": [_P, _P, _P, _I, _I, _L, _P],
+    "lb_embedding_fwd": [_P, _P, _P, _I, _I, _I, _I, _P],
+    "lb_embedding_bwd": [_P, _P, _P, _I, _I, _I, _I, _P],
+    "lb_ce_stats": [_P, _P, _P, _P, _P, _I, _I, _L, _I, _P],
+    "lb_ce_grad": [_P, _P, _P, _P, _P, _I, _I, _L, _I, _F, _I, _P],
+    "lb_adamw": [_P, _P, _P, _P, _P, _L, _F, _F, _F, _F, _F, _F, _F, _F, _I, _P],
+    "lb_sumsq": [_P, _L, _P, _I, _P],
+    "lb_add_inplace": [_P, _P, _L, _P],
+    "lb_gemm_bf16": [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _I, _P],
+    "lb_flash_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _P],
+    "lb_flash_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
+                     _L, _L, _L, _L, _L, _L, _L, _L, _F, _I, _P],
+}
+
+
+def _load() -> Optional[ctypes.CDLL]:
+    global _LIB, _LIB_ERR
+    if _LIB is not None or _LIB_ERR is not None:
+        return _LIB
+    path = lib_path()
+    if not os.path.exists(path):
+        _LIB_ERR = f"{path} not built (run: python -m lightron_b200.csrc.build)"
+        return None
+    try:
+        lib = ctypes.CDLL(path)
+    except OSError as e:  # pragma: no cover
+        _LIB_ERR = f"cannot load {path}: {e}"
+        return None
+    for name, args in _SIGNATURES.items():
+        fn = getattr(lib, name, None)
+        if fn is None:
+            continue
+        fn.argtypes = args
+        fn.restype = c_int
+    _LIB = lib
+    return _LIB
+
+
+def available() -> bool:
+    """True when CUDA kernels can run: a GPU is present and the library loads."""
+    return torch.cuda.is_available() and _load() is not None
+
+
+def require() -> ctypes.CDLL:
+    lib = _load()
+    if lib is None:
+        raise RuntimeError(f"lightron_b200 native kernels unavailable: {_LIB_ERR}")
+    return lib
+
+
+def use_native(t: torch.Tensor) -> bool:
+    """CUDA bf16 tensors take the native path; anything else the PyTorch oracle path.
+    On a GPU box the library must be present (loud failure instead of a silent fallback)."""
+    if not t.is_cuda or t.dtype != torch.bfloat16:
+        return False
+    require()
+    return True
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+_ERRORS = {-1: "invalid argument", -2: "CUDA launch error", -3: "unsupported shape", -4: "driver entry point missing",
+           -5: "tensor map encode failed", -6: "size exceeds static scratch capacity"}
+
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Number of native kernel entry points invoked so far in this process."""
+    return _LAUNCHES
+
+
+def call(name: str, *args) -> None:
+    global _LAUNCHES
+    lib = require()
+    rc = getattr(lib, name)(*args)
+    _LAUNCHES += 1
+    if rc != 0:
+        raise NativeError(f"{name} failed: {_ERRORS.get(rc, rc)} (cuda error {lib.lb_last_error()})")
