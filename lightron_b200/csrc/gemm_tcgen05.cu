@@ -1,0 +1,389 @@
+// bf16 GEMM for sm_100a:  C[M,N] = op(A) * op(B)^T with fp32 accumulation in tensor memory.
+//
+//   * operands are staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle,
+//     no cluster multicast) through a 4-stage mbarrier ring;
+//   * one elected thread issues tcgen05.mma (cta_group::1, kind::f16, 128x256x16 per
+//     instruction) with shared-memory matrix descriptors;
+//   * accumulators live in TMEM: 2 buffers x 256 columns, so the epilogue of tile i (tcgen05.ld ->
+//     bf16 -> global) overlaps the main loop of tile i+1;
+//   * persistent: one CTA per SM walks the tile list in an L2-friendly grouped order;
+//   * both operand majors are supported so that forward (x W^T), dgrad (dy W) and wgrad
+//     (dy^T x) all read the tensors as they sit in memory, with no transposes:
+//        a_mn = 0: A stored [M, K] (K contiguous)      a_mn = 1: A stored [K, M] (M contiguous)
+//        b_mn = 0: B stored [N, K] (K contiguous)      b_mn = 1: B stored [K, N] (N contiguous)
+//   * every mbarrier wait is bounded; on expiry the kernel records a status code, stops issuing
+//     work, frees its TMEM and returns.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer,
+// warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w%4) .. +31).
+#include <cuda.h>
+#include "common.cuh"
+
+// Device-side status words of the GEMM kernels.  A bounded wait that runs out sets word 0 to a
+// non-zero code and word 1 to a location id instead of spinning forever; the host reads them
+// with lb_device_status().
+static __device__ unsigned int g_lb_dev_status[4] = {0, 0, 0, 0};
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 20;
+constexpr int GROUP_M = 8;
+
+// ---- PTX wrappers -------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (and records where) when the limit is hit or another role has
+// already given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned where) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicExch(&g_lb_dev_status[0], 1u);
+  atomicExch(&g_lb_dev_status[1], where);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// Arrives on the mbarrier once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format, 128-byte swizzle).
+//   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4
+//   bits [32,46) stride byte offset >> 4   bits [46,48) version = 1      bits [61,64) layout = 2 (SWIZZLE_128B)
+// K-major tile  [rows][64 elems]: 8-row groups are 1024 B apart (SBO); LBO is unused (1).
+// MN-major tile [k rows][64 elems] per 64-wide MN group: groups are `lbo` bytes apart, 8-k-row
+// groups 1024 B apart (SBO).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+struct GemmParams {
+  int M, N, K;
+  long long ldc;
+  int a_mn, b_mn;
+  int tiles_m, tiles_n, num_tiles, num_kb;
+};
+
+__device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& tm, int& tn) {
+  const int group_size = GROUP_M * p.tiles_n;
+  const int group = t / group_size;
+  const int first_m = group * GROUP_M;
+  const int gsz = min(p.tiles_m - first_m, GROUP_M);
+  const int in_group = t - group * group_size;
+  tm = first_m + in_group % gsz;
+  tn = in_group / gsz;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 bf16* __restrict__ C, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  // bars: [0,STAGES) full, [STAGES,2*STAGES) empty, then tmem_full[2], tmem_empty[2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; a++) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+  }
+  if (warp == 1) {  // allocate all 512 TMEM columns (one CTA per SM by construction)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, p, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < p.num_kb; kb++) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1u)) { ok = false; break; }
+          const uint32_t fb = full_bar(stage);
+          mbar_expect_tx(fb, STAGE_BYTES);
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          const int k0 = kb * BK;
+          if (!p.a_mn) {
+            tma_load_2d(sa, &tmap_a, k0, m0, fb);                     // box {64 k, 128 m}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; j++) tma_load_2d(sa + j * 8192, &tmap_a, m0 + 64 * j, k0, fb);  // box {64 m, 64 k}
+          }
+          if (!p.b_mn) {
+            tma_load_2d(sb, &tmap_b, k0, n0, fb);                     // box {64 k, 256 n}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; j++) tma_load_2d(sb + j * 8192, &tmap_b, n0 + 64 * j, k0, fb);  // box {64 n, 64 k}
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      // instruction descriptor: D=f32, A=B=bf16, majors, N>>3 at bit 17, M>>4 at bit 24
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
+      const uint32_t a_kstep = p.a_mn ? 2048u : 32u, b_kstep = p.b_mn ? 2048u : 32u;  // bytes per K=16 slice
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x, it++) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, 2u)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
+        for (int kb = 0; kb < p.num_kb; kb++) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, 3u)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; k++) {
+            const uint64_t ad = make_desc(sa + k * a_kstep, a_lbo, 1024u);
+            const uint64_t bd = make_desc(sb + k * b_kstep, b_lbo, 1024u);
+            umma_bf16(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // frees this smem stage when the MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(tfull_bar(acc));  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (4 warps) ------------------------------
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may access
+    bool ok = true;
+    int it = 0;
+    for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x, it++) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      int tm, tn;
+      tile_coords(t, p, tm, tn);
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4u)) { ok = false; break; }
+      tcgen05_fence_after();
+      const int row = tm * BM + quad * 32 + lane;
+      const int n0 = tn * BN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * BN;
+      bf16* crow = C + (size_t)row * p.ldc + n0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c++) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (row < p.M) {
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            const int col = n0 + c * 32 + g * 8;
+            if (col < p.N) {  // N is a multiple of 8
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[g * 8 + i]);
+              *reinterpret_cast<uint4*>(crow + c * 32 + g * 8) = pack8(f);
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows of `ld` elements.
+int make_map(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
+             uint32_t box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return LB_ERR_DRIVER;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_lb_last_cuda_error = (int)r;
+    return LB_ERR_TMAP;
+  }
+  return LB_OK;
+}
+
+int g_num_sms = 0;
+
+}  // namespace
+
+// Copies the 4 status words to host memory `out` (synchronous) and clears them.
+extern "C" int lb_device_status(void* out) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_lb_dev_status, sizeof(unsigned int) * 4);
+  if (e != cudaSuccess) { g_lb_last_cuda_error = (int)e; return LB_ERR_LAUNCH; }
+  unsigned int zeros[4] = {0, 0, 0, 0};
+  cudaMemcpyToSymbol(g_lb_dev_status, zeros, sizeof(zeros));
+  return LB_OK;
+}
+
+// C[M,N] (row stride ldc) = op(A) op(B)^T, bf16 in / bf16 out, fp32 accumulate.
+// Requirements: A, B, C 16-byte aligned; lda, ldb, ldc, N multiples of 8 elements.
+extern "C" int lb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                            long long ldc, int a_mn, int b_mn, int flags, void* stream) {
+  (void)flags;
+  if (M <= 0 || N <= 0 || K <= 0) return LB_ERR_SHAPE;
+  if ((lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8)) return LB_ERR_SHAPE;
+  if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return LB_ERR_ARG;
+  if (a_mn && (M % 8)) return LB_ERR_SHAPE;
+  CUtensorMap ta, tb;
+  int rc;
+  if (!a_mn) rc = make_map(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM);
+  else       rc = make_map(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK);
+  if (rc) return rc;
+  if (!b_mn) rc = make_map(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, BN);
+  else       rc = make_map(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK);
+  if (rc) return rc;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  }
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.a_mn = a_mn; p.b_mn = b_mn;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.num_kb = (K + BK - 1) / BK;
+  int grid = p.num_tiles < g_num_sms ? p.num_tiles : g_num_sms;
+  gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, (bf16*)C, p);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}

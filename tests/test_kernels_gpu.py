@@ -1,0 +1,252 @@
+"""Numerics of every CUDA kernel against a plain PyTorch fp32 restatement of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _rand(*shape, scale=1.0, dtype=torch.bfloat16, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device="cuda", dtype=torch.float32) * scale).to(dtype)
+
+
+def _gemm_status():
+    import ctypes
+    from lightron_b200.ops import native
+    buf = (ctypes.c_uint * 4)()
+    native.require().lb_device_status(ctypes.cast(buf, ctypes.c_void_p))
+    return list(buf)
+
+
+def _rel_err(got, want):
+    return ((got.float() - want.float()).norm() / want.float().norm().clamp_min(1e-12)).item()
+
+
+# ---- GEMM -------------------------------------------------------------------------------------
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)],
+                         ids=["kk", "kmn", "mnmn", "mnk"])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 264, 200), (1000, 1032, 520), (4096, 2560, 2048)])
+def test_gemm_all_majors(M, N, K, a_mn, b_mn):
+    from lightron_b200.ops import functional as OF
+    if a_mn and M % 8:
+        pytest.skip("MN-major A needs M % 8 == 0")
+    a = _rand(M, K, seed=1)
+    b = _rand(N, K, seed=2)
+    want = a.float() @ b.float().t()
+    a_arg = a.t().contiguous() if a_mn else a
+    b_arg = b.t().contiguous() if b_mn else b
+    got = OF.gemm(a_arg, b_arg, a_mn=a_mn, b_mn=b_mn)
+    torch.cuda.synchronize()
+    st = _gemm_status()
+    assert st[0] == 0, f"device status {st}"
+    err = _rel_err(got, want)
+    assert err < 5e-3, f"rel err {err} (a_mn={a_mn}, b_mn={b_mn}, {M}x{N}x{K}); max abs {(got.float()-want).abs().max().item()}"
+
+
+def test_gemm_strided_operands_and_output():
+    from lightron_b200.ops import functional as OF
+    big = _rand(512, 1024, seed=3)
+    a = big[:, 256:768]                      # row stride 1024, K = 512
+    w = _rand(384, 512, seed=4)
+    out_big = torch.zeros(512, 1024, dtype=torch.bfloat16, device="cuda")
+    out = out_big[:, 128:512]
+    OF.gemm(a, w, out=out)
+    torch.cuda.synchronize()
+    want = a.float() @ w.float().t()
+    assert _rel_err(out, want) < 5e-3
+    assert out_big[:, :128].abs().max().item() == 0 and out_big[:, 512:].abs().max().item() == 0
+
+
+def test_linear_autograd_fused_weights():
+    from lightron_b200.ops import functional as OF
+    T, K = 512, 256
+    x = _rand(T, K, seed=5).requires_grad_(True)
+    flat = _rand(3 * 128 * K, scale=0.05, seed=6)
+    ws = [flat[i * 128 * K:(i + 1) * 128 * K].view(128, K).requires_grad_(True) for i in range(3)]
+    assert OF._rows_adjacent(ws)
+    y = OF.linear(x, *ws)
+    dy = _rand(T, 384, seed=7)
+    y.backward(dy)
+    xf = x.detach().float().requires_grad_(True)
+    wf = [w.detach().float().requires_grad_(True) for w in ws]
+    yf = torch.cat([xf @ w.t() for w in wf], dim=1)
+    yf.backward(dy.float())
+    assert _rel_err(y, yf) < 5e-3
+    assert _rel_err(x.grad, xf.grad) < 5e-3
+    for w, wr in zip(ws, wf):
+        assert _rel_err(w.grad, wr.grad) < 5e-3
+
+
+# ---- elementwise ------------------------------------------------------------------------------------
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 256), (1000, 2048), (333, 4096)])
+def test_rmsnorm_fwd_bwd(rows, cols):
+    from lightron_b200.ops import functional as OF, reference as ref
+    x = _rand(rows, cols, seed=1).requires_grad_(True)
+    w = (1 + 0.1 * _rand(cols, seed=2).float()).to(torch.bfloat16).requires_grad_(True)
+    y = OF.rmsnorm(x, w, 1e-5)
+    dy = _rand(rows, cols, seed=3)
+    y.backward(dy)
+    xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yf = ref.rmsnorm(xf, wf, 1e-5)
+    yf.backward(dy.float())
+    assert _rel_err(y, yf) < 5e-3
+    assert _rel_err(x.grad, xf.grad) < 1e-2
+    assert _rel_err(w.grad, wf.grad) < 1e-2
+
+
+def test_add_rmsnorm_fwd_bwd():
+    from lightron_b200.ops import functional as OF, reference as ref
+    rows, cols = 512, 2048
+    x = _rand(rows, cols, seed=1).requires_grad_(True)
+    r = _rand(rows, cols, seed=2).requires_grad_(True)
+    w = (1 + 0.1 * _rand(cols, seed=3).float()).to(torch.bfloat16).requires_grad_(True)
+    h, y = OF.add_rmsnorm(x, r, w, 1e-5)
+    dh, dy = _rand(rows, cols, seed=4), _rand(rows, cols, seed=5)
+    torch.autograd.backward([h, y], [dh, dy])
+    xf, rf, wf = (t.detach().float().requires_grad_(True) for t in (x, r, w))
+    hf = xf + rf
+    yf = ref.rmsnorm(hf, wf, 1e-5)
+    torch.autograd.backward([hf, yf], [dh.float(), dy.float()])
+    assert _rel_err(h, hf) < 5e-3 and _rel_err(y, yf) < 5e-3
+    assert _rel_err(x.grad, xf.grad) < 1e-2 and _rel_err(r.grad, rf.grad) < 1e-2
+    assert _rel_err(w.grad, wf.grad) < 1e-2
+
+
+@pytest.mark.parametrize("d", [32, 64, 128])
+def test_rope_matches_complex_reference(d):
+    from lightron_b200.ops import functional as OF, reference as ref
+    B, S, h = 2, 96, 4
+    x = _rand(B, S, h, d, seed=1).requires_grad_(True)
+    cos, sin = ref.rope_tables(d, 128, 10000.0, device="cuda")
+    pos = torch.arange(S, device="cuda").flip(0).to(torch.int32).contiguous()
+    for positions in (None, pos):
+        x.grad = None
+        y = OF.rope(x, cos, sin, positions)
+        dy = _rand(B, S, h, d, seed=2)
+        y.backward(dy)
+        # complex-number oracle (the reference's formulation, layers/layers.py:44-70)
+        ang = torch.outer((torch.arange(S, device="cuda") if positions is None else positions).float(),
+                          1.0 / (10000.0 ** (torch.arange(0, d, 2, device="cuda").float() / d)))
+        fc = torch.polar(torch.ones_like(ang), ang).view(1, S, 1, d // 2)
+        xf = x.detach().float().requires_grad_(True)
+        yc = torch.view_as_real(torch.view_as_complex(xf.reshape(B, S, h, d // 2, 2)) * fc).flatten(3)
+        yc.backward(dy.float())
+        assert _rel_err(y, yc) < 5e-3
+        assert _rel_err(x.grad, xf.grad) < 5e-3
+
+
+def test_swiglu_fwd_bwd():
+    from lightron_b200.ops import functional as OF
+    rows, I = 300, 688
+    gu = _rand(rows, 2 * I, seed=1).requires_grad_(True)
+    y = OF.swiglu(gu)
+    dy = _rand(rows, I, seed=2)
+    y.backward(dy)
+    gf = gu.detach().float().requires_grad_(True)
+    yf = torch.nn.functional.silu(gf[:, :I]) * gf[:, I:]
+    yf.backward(dy.float())
+    assert _rel_err(y, yf) < 5e-3
+    assert _rel_err(gu.grad, gf.grad) < 1e-2
+
+
+def test_embedding_fwd_bwd_vocab_parallel():
+    from lightron_b200.ops import functional as OF
+    V, H, T = 1000, 256, 4096
+    w = _rand(500, H, seed=1).requires_grad_(True)         # holds vocab ids [250, 750)
+    tok = torch.randint(0, V, (8, T // 8), device="cuda")
+    y = OF.embedding(tok, w, 250)
+    dy = _rand(8, T // 8, H, seed=2)
+    y.backward(dy)
+    wf = w.detach().float().requires_grad_(True)
+    local = tok - 250
+    mask = (local < 0) | (local >= 500)
+    yf = torch.nn.functional.embedding(local.clamp(0, 499), wf) * (~mask).unsqueeze(-1)
+    yf.backward(dy.float())
+    assert torch.equal(y.float(), yf.detach())
+    assert _rel_err(w.grad, wf.grad) < 2e-2           # bf16 atomics accumulate with rounding
+
+
+@pytest.mark.parametrize("T,V", [(257, 8192), (1024, 32000)])
+def test_cross_entropy_fwd_bwd(T, V):
+    from lightron_b200.ops import functional as OF
+    logits = _rand(T, V, scale=2.0, seed=1)
+    tgt = torch.randint(0, V, (T,), device="cuda")
+    lf = logits.float().requires_grad_(True)
+    want = torch.nn.functional.cross_entropy(lf, tgt)
+    (want * 0.5).backward()
+    lg = logits.clone().requires_grad_(True)
+    got = OF.cross_entropy(lg * 1.0, tgt, n_valid_total=T)
+    (got * 0.5).backward()
+    assert abs(got.item() - want.item()) < 2e-3 * max(1.0, abs(want.item()))
+    assert _rel_err(lg.grad, lf.grad) < 2e-2
+
+
+def test_adamw_matches_torch():
+    from lightron_b200.ops import native
+    n = 1 << 16
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda").to(torch.bfloat16)
+    ref_p = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref_p], lr=1e-2, weight_decay=0.1)
+    master, m, v = p.clone(), torch.zeros_like(p), torch.zeros_like(p)
+    out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    for step in range(1, 4):
+        ref_p.grad = g.float()
+        opt.step()
+        native.call("lb_adamw", master.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), out.data_ptr(), n,
+                    1e-2, 0.9, 0.999, 1e-8, 0.1, 1 - 0.9 ** step, 1 - 0.999 ** step, 1.0, 0, native.stream_ptr())
+    torch.cuda.synchronize()
+    assert torch.allclose(master, ref_p.detach(), atol=1e-5, rtol=1e-4)
+    assert torch.equal(out, master.to(torch.bfloat16))
+
+
+# ---- attention ------------------------------------------------------------------------------------
+
+
+@pytest.mark.parametrize("d", [32, 64, 128])
+@pytest.mark.parametrize("B,Sq,Sk,hq,hkv,causal", [
+    (2, 128, 128, 4, 4, True), (1, 256, 256, 8, 2, True), (2, 200, 200, 4, 1, True),
+    (1, 192, 320, 4, 2, False), (1, 128, 64, 2, 2, False), (1, 64, 192, 2, 1, True),
+])
+def test_flash_attention_fwd_bwd(B, Sq, Sk, hq, hkv, causal, d):
+    from lightron_b200.ops import functional as OF, reference as ref
+    q = _rand(B, Sq, hq, d, seed=1).requires_grad_(True)
+    k = _rand(B, Sk, hkv, d, seed=2).requires_grad_(True)
+    v = _rand(B, Sk, hkv, d, seed=3).requires_grad_(True)
+    o = OF.flash_attention(q, k, v, causal)
+    do = _rand(B, Sq, hq, d, seed=4)
+    o.backward(do)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    of = ref.attention(qf, kf, vf, causal=causal)
+    of.backward(do.float())
+    assert _rel_err(o, of) < 1e-2, f"fwd {_rel_err(o, of)}"
+    assert _rel_err(q.grad, qf.grad) < 2e-2, f"dq {_rel_err(q.grad, qf.grad)}"
+    assert _rel_err(k.grad, kf.grad) < 2e-2, f"dk {_rel_err(k.grad, kf.grad)}"
+    assert _rel_err(v.grad, vf.grad) < 2e-2, f"dv {_rel_err(v.grad, vf.grad)}"
+
+
+def test_rope_attention_on_fused_qkv():
+    from lightron_b200.ops import functional as OF, reference as ref
+    B, S, hq, hkv, d = 2, 256, 8, 2, 64
+    width = (hq + 2 * hkv) * d
+    base = _rand(B * S, width, seed=1)
+    cos, sin = ref.rope_tables(d, S, 10000.0, device="cuda")
+    x = base.clone().requires_grad_(True)
+    o = OF.rope_attention_qkv(x * 1.0, cos, sin, None, B, S, hq, hkv, d)
+    do = _rand(B * S, hq * d, seed=2)
+    o.backward(do)
+    xf = base.float().requires_grad_(True)
+    of = OF.rope_attention_qkv(xf, cos, sin, None, B, S, hq, hkv, d)     # fp32 tensors take the oracle path
+    of.backward(do.float())
+    assert _rel_err(o, of) < 1e-2
+    assert _rel_err(x.grad, xf.grad) < 2e-2
