@@ -95,6 +95,10 @@ PRESETS: Dict[str, Dict[str, Any]] = {
                  intermediate_size=688, norm_eps=1e-5, rope_theta=10000.0),
     "llama-1.1b": dict(dim=2048, n_layers=22, n_heads=32, n_kv_heads=4, vocab_size=32000,
                        intermediate_size=5632, norm_eps=1e-5, rope_theta=10000.0),
+    # the 1.1B shape with as many KV heads as query heads: the nearest shape that the reference's
+    # stock attention (no GQA) can run; used for like-for-like comparisons only
+    "llama-1.1b-mha": dict(dim=2048, n_layers=22, n_heads=32, n_kv_heads=32, vocab_size=32000,
+                           intermediate_size=5632, norm_eps=1e-5, rope_theta=10000.0),
     "llama-8b": dict(dim=4096, n_layers=32, n_heads=32, n_kv_heads=8, vocab_size=128256,
                      intermediate_size=14336, norm_eps=1e-5, rope_theta=500000.0),
     "moe-8x": dict(dim=4096, n_layers=16, n_heads=32, n_kv_heads=8, vocab_size=32000,

@@ -362,6 +362,13 @@ extern "C" int lb_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   if ((lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8)) return LB_ERR_SHAPE;
   if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return LB_ERR_ARG;
   if (a_mn && (M % 8)) return LB_ERR_SHAPE;
+  // The driver-API encode call needs a current context on THIS thread; autograd's backward
+  // threads may not have touched the runtime yet.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(0);
+    ctx_bound = true;
+  }
   CUtensorMap ta, tb;
   int rc;
   if (!a_mn) rc = make_map(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM);
