@@ -519,3 +519,61 @@ extern "C" int lb_add_inplace(void* a, const void* b, long long n, void* stream)
   LB_CHECK_LAUNCH();
   return LB_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm backward for callers that must not allocate.
+//
+// lb_rmsnorm_bwd() above needs a caller-provided `partial` scratch of [blocks, cols] floats.
+// A caller that lives inside an allocator hook, a signal-safe teardown path, a process whose
+// memory pool is frozen after start-up, or a plain C host that links this library without
+// PyTorch's caching allocator has nowhere to get that buffer from, so this variant keeps the
+// scratch in a fixed array in device memory that is part of the library image itself.
+//
+//  * Capacity: cols <= 8192 and at most 128 blocks, i.e. 4 MiB of fp32.  Every GPU on which
+//    the library is loaded holds these 4 MiB until the process exits.  A larger `cols` is
+//    rejected with LB_ERR_CAPACITY (-6); nothing is launched in that case.
+//  * The first call on a device looks up the array's device address (cudaGetSymbolAddress,
+//    with that device current) and remembers it per device.  Make that first call before
+//    starting any stream capture.
+//  * Nothing is allocated or freed here, by CUDA or by any library.
+//  * The array is shared by every call and keeps the previous call's contents.  Each call
+//    overwrites all rows that it later reads (one row per launched block), so nothing has to be
+//    cleared first.  Two calls that can run at the same time on one GPU (different streams,
+//    different threads) write the same rows and race: serialise them.
+//  * Inputs, outputs and results are those of lb_rmsnorm_bwd; only the summation order over
+//    blocks may differ (fewer, larger blocks), which changes dw by fp32 rounding only.
+// ---------------------------------------------------------------------------------------
+#define LB_STATIC_SCRATCH_MAX_COLS 8192
+#define LB_STATIC_SCRATCH_MAX_BLOCKS 128
+static __device__ __align__(256) float g_rmsnorm_static_scratch[LB_STATIC_SCRATCH_MAX_BLOCKS * LB_STATIC_SCRATCH_MAX_COLS];
+
+#define LB_MAX_DEVICES 64
+static float* g_static_scratch_addr[LB_MAX_DEVICES] = {nullptr};
+
+extern "C" int lb_rmsnorm_bwd_static(const void* dy, const void* x, const void* w, const void* rstd, const void* dres,
+                                     void* dx, void* dw, int rows, int cols, void* stream) {
+  if (cols % 8 || rows <= 0) return LB_ERR_SHAPE;
+  if (cols > LB_STATIC_SCRATCH_MAX_COLS) return LB_ERR_CAPACITY;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= LB_MAX_DEVICES) { g_lb_last_cuda_error = (int)e; return LB_ERR_ARG; }
+  if (g_static_scratch_addr[dev] == nullptr) {
+    // In host code the array's name is only a handle; the kernel needs its device address.
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_rmsnorm_static_scratch);
+    if (e != cudaSuccess || p == nullptr) { g_lb_last_cuda_error = (int)e; return LB_ERR_LAUNCH; }
+    g_static_scratch_addr[dev] = p;
+  }
+  float* partial = g_static_scratch_addr[dev];
+  int nblk = lb_rmsnorm_bwd_blocks(rows, cols);
+  if (nblk > LB_STATIC_SCRATCH_MAX_BLOCKS) nblk = LB_STATIC_SCRATCH_MAX_BLOCKS;
+  cudaStream_t s = (cudaStream_t)stream;
+  size_t smem = (size_t)cols * sizeof(float);
+  if (smem > 48 * 1024) cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  rmsnorm_bwd_kernel<<<nblk, 256, smem, s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)rstd,
+                                             (const bf16*)dres, (bf16*)dx, partial, rows, cols);
+  LB_CHECK_LAUNCH();
+  rmsnorm_dw_reduce_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial, (bf16*)dw, nblk, cols);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}
