@@ -1,0 +1,452 @@
+// FlashAttention backward on the 5th-generation tensor cores (sm_100a), head_dim 64 or 128.
+//
+// One CTA owns a block of 128 keys of one (batch, kv head) and walks over every 128-query block
+// (of every query head of the GQA group) that can see it.  Per query block, five tcgen05 MMAs:
+//     S   = Q K^T            [128 q x 128 k]   (K-major operands)
+//     dP  = dO V^T           [128 q x 128 k]
+//     dV += P^T dO           [128 k x d]       A = P as MN-major operand, B = dO MN-major
+//     dK += dS^T Q           [128 k x d]       A = dS MN-major, B = Q MN-major
+//     dQ  = dS K             [128 q x d]       A = dS K-major,  B = K MN-major
+// S, dP, dQ, dV, dK live in TMEM (dV / dK accumulate there across the whole loop, so no
+// rescaling is ever needed).  256 "softmax" threads (8 warps; thread = one query row x half of
+// the columns) read S and dP with tcgen05.ld, form P = exp(scale S - lse) and
+// dS = P (dP - delta) scale in registers, and write both as bf16 into 128B-swizzled shared
+// memory, where the same bytes serve as K-major (dQ) and MN-major (dV, dK) MMA operands.
+// dQ tiles are added to an fp32 accumulator in global memory with vector atomics.
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-9 math.
+// With head_dim 128 the dQ tile aliases the dP columns (TMEM is 512 columns) and Q/dO are
+// single-buffered; with head_dim 64 Q/dO are double-buffered and S/dP of the next query block
+// are issued while the current one is still in the math warps.
+// All waits are bounded; on expiry a status word is set and the CTA drains and frees its TMEM.
+#include "tcgen05.cuh"
+
+static __device__ unsigned int g_fab_status[4] = {0, 0, 0, 0};
+
+namespace {
+using namespace bw;
+
+struct FaBwdParams {
+  const bf16 *o, *dout;
+  const float* lse;
+  float *delta, *dq_acc;
+  bf16 *dq, *dk, *dv;
+  int B, Sq, Sk, hq, hkv;
+  long long o_ts, do_ts, dq_ts, dk_ts, dv_ts;
+  float scale;
+  int causal;
+};
+
+template <int D>
+struct BwdCfg {
+  static constexpr int BM = 128, BN = 128;
+  static constexpr int ST = (D == 64) ? 2 : 1;          // Q/dO stages
+  static constexpr bool EARLY = (D == 64);              // issue S/dP of block i+1 before dV/dK/dQ of block i
+  static constexpr int ATOMS = D / 64;
+  static constexpr int ATOM_BYTES = 128 * 128;
+  static constexpr int TILE_BYTES = ATOMS * ATOM_BYTES;
+  static constexpr int P_BYTES = 2 * ATOM_BYTES;
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = OFF_K + TILE_BYTES;
+  static constexpr int OFF_Q = OFF_V + TILE_BYTES;              // [ST]
+  static constexpr int OFF_DO = OFF_Q + ST * TILE_BYTES;        // [ST]
+  static constexpr int OFF_P = OFF_DO + ST * TILE_BYTES;
+  static constexpr int OFF_DS = OFF_P + P_BYTES;
+  static constexpr int OFF_BAR = OFF_DS + P_BYTES;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;
+  static constexpr int NBAR = 1 + 2 * ST + 5;
+  // TMEM columns
+  static constexpr int COL_S = 0, COL_DP = 128;
+  static constexpr int COL_DQ = (D == 64) ? 256 : 128;          // aliases dP for d = 128
+  static constexpr int COL_DV = (D == 64) ? 320 : 256;
+  static constexpr int COL_DK = (D == 64) ? 384 : 384;
+};
+
+template <int D>
+__global__ void fa_delta_kernel(const FaBwdParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)p.B * p.Sq * p.hq;
+  for (long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); idx < total;
+       idx += (long long)gridDim.x * (blockDim.x >> 5)) {
+    const int h = (int)(idx % p.hq);
+    const long long bi = idx / p.hq;
+    const bf16* o = p.o + bi * p.o_ts + (long long)h * D;
+    const bf16* d = p.dout + bi * p.do_ts + (long long)h * D;
+    float s = 0.f;
+    for (int c = lane * 2; c < D; c += 64) {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const bf162*>(o + c));
+      const float2 e = __bfloat1622float2(*reinterpret_cast<const bf162*>(d + c));
+      s += a.x * e.x + a.y * e.y;
+    }
+    s = warp_sum(s);
+    if (lane == 0) {
+      const int b = (int)(bi / p.Sq), i = (int)(bi % p.Sq);
+      p.delta[((long long)b * p.hq + h) * p.Sq + i] = s;
+    }
+  }
+}
+
+template <int D>
+__global__ void fa_dq_convert_kernel(const FaBwdParams p) {
+  constexpr int VPR = D / 8;
+  const long long total = (long long)p.B * p.Sq * p.hq * VPR;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(idx % VPR);
+    const long long th = idx / VPR;
+    const int h = (int)(th % p.hq);
+    const long long bi = th / p.hq;
+    const float4* src = reinterpret_cast<const float4*>(p.dq_acc + (bi * p.hq + h) * D + v * 8);
+    const float4 a = src[0], c = src[1];
+    const float f[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
+    *reinterpret_cast<uint4*>(p.dq + bi * p.dq_ts + (long long)h * D + v * 8) = pack8(f);
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(320, 1)
+fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                 const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo, const FaBwdParams p) {
+  using C = BwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NBAR);
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t kv_full = bar0;
+  auto qdo_full = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto qdo_empty = [&](int s) { return bar0 + 8u * (1 + C::ST + s); };
+  const uint32_t bar1 = bar0 + 8u * (1 + 2 * C::ST);
+  const uint32_t sdp_full = bar1, sdp_free = bar1 + 8, pds_full = bar1 + 16, dq_full = bar1 + 24, dq_free = bar1 + 32;
+
+  const int nblk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int n0 = nblk * C::BN;
+  const int off = p.Sk - p.Sq;
+  const int rep = p.hq / p.hkv;
+  const int n_mblocks = (p.Sq + C::BM - 1) / C::BM;
+  int mb_first = 0;
+  if (p.causal) {
+    const int first_row = n0 - off;
+    mb_first = first_row > 0 ? first_row / C::BM : 0;
+  }
+  const int per_head = n_mblocks > mb_first ? n_mblocks - mb_first : 0;
+  const int total_it = per_head * rep;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < C::ST; s++) { mbar_init(qdo_full(s), 1); mbar_init(qdo_empty(s), 1); }
+    mbar_init(sdp_full, 1);
+    mbar_init(sdp_free, 256);
+    mbar_init(pds_full, 256);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_free, 256);
+    mbar_init_fence();
+    prefetch_tmap(&tq); prefetch_tmap(&tk); prefetch_tmap(&tv); prefetch_tmap(&tdo);
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0 && total_it > 0) {
+      mbar_expect_tx(kv_full, 2 * C::TILE_BYTES);
+#pragma unroll
+      for (int a = 0; a < C::ATOMS; a++) {
+        tma_load_2d(sbase + C::OFF_K + a * C::ATOM_BYTES, &tk, hk * D + a * 64, b * p.Sk + n0, kv_full);
+        tma_load_2d(sbase + C::OFF_V + a * C::ATOM_BYTES, &tv, hk * D + a * 64, b * p.Sk + n0, kv_full);
+      }
+      bool ok = true;
+      for (int it = 0; it < total_it; it++) {
+        const int st = it % C::ST;
+        const int h = hk * rep + it / per_head;
+        const int m0 = (mb_first + it % per_head) * C::BM;
+        if (!mbar_wait(qdo_empty(st), (((uint32_t)(it / C::ST)) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(qdo_full(st), 2 * C::TILE_BYTES);
+#pragma unroll
+        for (int a = 0; a < C::ATOMS; a++) {
+          tma_load_2d(sbase + C::OFF_Q + st * C::TILE_BYTES + a * C::ATOM_BYTES, &tq, h * D + a * 64, b * p.Sq + m0, qdo_full(st));
+          tma_load_2d(sbase + C::OFF_DO + st * C::TILE_BYTES + a * C::ATOM_BYTES, &tdo, h * D + a * 64, b * p.Sq + m0, qdo_full(st));
+        }
+      }
+      if (!ok) atomicExch(&g_fab_status[0], 1u);
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0 && total_it > 0) {
+      const uint32_t idesc_s = make_idesc(128, 128, 0, 0);     // S, dP: K-major A and B
+      const uint32_t idesc_kv = make_idesc(128, D, 1, 1);      // dV, dK: MN-major A and B
+      const uint32_t idesc_dq = make_idesc(128, D, 0, 1);      // dQ: K-major A, MN-major B
+      const uint32_t sK = sbase + C::OFF_K, sV = sbase + C::OFF_V, sP = sbase + C::OFF_P, sDS = sbase + C::OFF_DS;
+      auto issue_s_dp = [&](int st) {
+        const uint32_t sQ = sbase + C::OFF_Q + st * C::TILE_BYTES, sDO = sbase + C::OFF_DO + st * C::TILE_BYTES;
+#pragma unroll
+        for (int s = 0; s < D / 16; s++) {
+          const uint32_t o = (s >> 2) * C::ATOM_BYTES + (s & 3) * 32;
+          umma_bf16(tmem_base + C::COL_S, make_desc(sQ + o, 16, 1024), make_desc(sK + o, 16, 1024), idesc_s, s ? 1u : 0u);
+        }
+#pragma unroll
+        for (int s = 0; s < D / 16; s++) {
+          const uint32_t o = (s >> 2) * C::ATOM_BYTES + (s & 3) * 32;
+          umma_bf16(tmem_base + C::COL_DP, make_desc(sDO + o, 16, 1024), make_desc(sV + o, 16, 1024), idesc_s, s ? 1u : 0u);
+        }
+        umma_commit(sdp_full);
+      };
+      auto issue_grads = [&](int st, int it) {
+        const uint32_t sQ = sbase + C::OFF_Q + st * C::TILE_BYTES, sDO = sbase + C::OFF_DO + st * C::TILE_BYTES;
+#pragma unroll
+        for (int s = 0; s < C::BM / 16; s++)      // dV += P^T dO   (K = 128 queries)
+          umma_bf16(tmem_base + C::COL_DV, make_desc(sP + s * 2048, C::ATOM_BYTES, 1024),
+                    make_desc(sDO + s * 2048, C::ATOM_BYTES, 1024), idesc_kv, (it | s) ? 1u : 0u);
+#pragma unroll
+        for (int s = 0; s < C::BM / 16; s++)      // dK += dS^T Q
+          umma_bf16(tmem_base + C::COL_DK, make_desc(sDS + s * 2048, C::ATOM_BYTES, 1024),
+                    make_desc(sQ + s * 2048, C::ATOM_BYTES, 1024), idesc_kv, (it | s) ? 1u : 0u);
+#pragma unroll
+        for (int s = 0; s < C::BN / 16; s++)      // dQ = dS K      (K = 128 keys)
+          umma_bf16(tmem_base + C::COL_DQ, make_desc(sDS + (s >> 2) * C::ATOM_BYTES + (s & 3) * 32, 16, 1024),
+                    make_desc(sK + s * 2048, C::ATOM_BYTES, 1024), idesc_dq, s ? 1u : 0u);
+        umma_commit(dq_full);
+        umma_commit(qdo_empty(st));
+      };
+      bool ok = mbar_wait(kv_full, 0, abort_flag);
+      if (ok) ok = mbar_wait(qdo_full(0), 0, abort_flag);
+      if (ok) {
+        fence_after();
+        issue_s_dp(0);
+      }
+      for (int it = 0; it < total_it && ok; it++) {
+        const int st = it % C::ST;
+        if (C::EARLY && it + 1 < total_it) {
+          const int st1 = (it + 1) % C::ST;
+          if (!mbar_wait(qdo_full(st1), ((uint32_t)((it + 1) / C::ST)) & 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(sdp_free, (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
+          fence_after();
+          issue_s_dp(st1);
+        }
+        if (!mbar_wait(pds_full, (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
+        if (it > 0 && !mbar_wait(dq_free, (uint32_t)(it - 1) & 1u, abort_flag)) { ok = false; break; }
+        fence_after();
+        issue_grads(st, it);
+        if (!C::EARLY && it + 1 < total_it) {
+          const int st1 = (it + 1) % C::ST;
+          if (!mbar_wait(qdo_full(st1), ((uint32_t)((it + 1) / C::ST)) & 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(dq_free, (uint32_t)it & 1u, abort_flag)) { ok = false; break; }   // dQ aliases dP
+          fence_after();
+          issue_s_dp(st1);
+        }
+      }
+      if (!ok) atomicExch(&g_fab_status[0], 2u);
+    }
+  } else {
+    // ------------------------------- math warps -------------------------------
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;               // which 64 of the 128 key columns / which half of d
+    const int rit = quad * 32 + lane;               // row inside the 128-row tile
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const float sl2 = p.scale * 1.4426950408889634f;
+    const float l2e = 1.4426950408889634f;
+    uint8_t* sPh = smem + C::OFF_P + half * C::ATOM_BYTES;
+    uint8_t* sDSh = smem + C::OFF_DS + half * C::ATOM_BYTES;
+    constexpr int DH = D / 2;                        // dQ / dK / dV columns per thread
+    bool ok = true;
+    int prev_row = 0, prev_h = 0;
+    auto flush_dq = [&](int it_prev) -> bool {
+      // dQ of the previous query block: TMEM -> fp32 atomics
+      if (!mbar_wait(dq_full, (uint32_t)it_prev & 1u, abort_flag)) return false;
+      fence_after();
+      float* dst = p.dq_acc + (((long long)b * p.Sq + prev_row) * p.hq + prev_h) * D + half * DH;
+#pragma unroll 1
+      for (int c = 0; c < DH / 32; c++) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + C::COL_DQ + half * DH + c * 32, r);
+        tmem_ld_wait();
+        if (prev_row < p.Sq) {
+#pragma unroll
+          for (int g = 0; g < 8; g++)
+            atomicAdd(reinterpret_cast<float4*>(dst + c * 32 + g * 4),
+                      make_float4(__uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]), __uint_as_float(r[g * 4 + 2]),
+                                  __uint_as_float(r[g * 4 + 3])));
+        }
+      }
+      fence_before();
+      mbar_arrive(dq_free);
+      return true;
+    };
+    for (int it = 0; it < total_it; it++) {
+      const int h = hk * rep + it / per_head;
+      const int m0 = (mb_first + it % per_head) * C::BM;
+      const int row = m0 + rit;
+      float lse_r = INFINITY, delta_r = 0.f;
+      if (row < p.Sq) {
+        const long long li = ((long long)b * p.hq + h) * p.Sq + row;
+        lse_r = p.lse[li];
+        delta_r = p.delta[li];
+      }
+      if (!mbar_wait(sdp_full, (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
+      fence_after();
+      uint32_t sr[64], dr[64];
+      tmem_ld32(lane_addr + C::COL_S + half * 64, sr);
+      tmem_ld32(lane_addr + C::COL_S + half * 64 + 32, sr + 32);
+      tmem_ld32(lane_addr + C::COL_DP + half * 64, dr);
+      tmem_ld32(lane_addr + C::COL_DP + half * 64 + 32, dr + 32);
+      tmem_ld_wait();
+      fence_before();
+      mbar_arrive(sdp_free);
+      // P and dS for this thread's 64 keys
+      const int key0 = n0 + half * 64;
+      const bool need_mask = (n0 + C::BN > p.Sk) || (p.causal && (n0 + C::BN - 1 > m0 + quad * 32 + off));
+      const int lim = p.causal ? min(p.Sk - 1, row + off) : p.Sk - 1;
+      const float nl = -lse_r * l2e;
+      uint32_t pp[32], dd[32];
+#pragma unroll
+      for (int i = 0; i < 64; i += 2) {
+        float p0 = exp2f(fmaf(__uint_as_float(sr[i]), sl2, nl));
+        float p1 = exp2f(fmaf(__uint_as_float(sr[i + 1]), sl2, nl));
+        if (need_mask) {
+          if (key0 + i > lim) p0 = 0.f;
+          if (key0 + i + 1 > lim) p1 = 0.f;
+        }
+        const float d0 = p0 * (__uint_as_float(dr[i]) - delta_r) * p.scale;
+        const float d1 = p1 * (__uint_as_float(dr[i + 1]) - delta_r) * p.scale;
+        bf162 pb = __floats2bfloat162_rn(p0, p1), db = __floats2bfloat162_rn(d0, d1);
+        pp[i >> 1] = *reinterpret_cast<uint32_t*>(&pb);
+        dd[i >> 1] = *reinterpret_cast<uint32_t*>(&db);
+      }
+      // P/dS smem may be rewritten only after the previous block's dV/dK/dQ MMAs have read it; the
+      // dq_full wait inside flush_dq() of that block guarantees it in both schedules.
+      if (C::EARLY && it > 0) {
+        if (!flush_dq(it - 1)) { ok = false; break; }
+      }
+#pragma unroll
+      for (int c = 0; c < 8; c++) {
+        const uint32_t o = sw128_off(rit, c);
+        *reinterpret_cast<uint4*>(sPh + o) = make_uint4(pp[c * 4], pp[c * 4 + 1], pp[c * 4 + 2], pp[c * 4 + 3]);
+        *reinterpret_cast<uint4*>(sDSh + o) = make_uint4(dd[c * 4], dd[c * 4 + 1], dd[c * 4 + 2], dd[c * 4 + 3]);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(pds_full);
+      prev_row = row;
+      prev_h = h;
+      if (!C::EARLY) {   // dQ aliases dP: it must be drained before the next S/dP can be issued
+        if (!flush_dq(it)) { ok = false; break; }
+      }
+    }
+    if (C::EARLY && ok && total_it > 0) ok = flush_dq(total_it - 1);
+    if (ok && total_it > 0) {
+      // dq_full of the last block was committed after every MMA: dV and dK are final
+      const int key = n0 + rit;
+      bf16* dkrow = p.dk + ((long long)b * p.Sk + key) * p.dk_ts + (long long)hk * D + half * DH;
+      bf16* dvrow = p.dv + ((long long)b * p.Sk + key) * p.dv_ts + (long long)hk * D + half * DH;
+#pragma unroll 1
+      for (int c = 0; c < DH / 32; c++) {
+        uint32_t r[32];
+        float f[32];
+        tmem_ld32(lane_addr + C::COL_DK + half * DH + c * 32, r);
+        tmem_ld_wait();
+        if (key < p.Sk) {
+#pragma unroll
+          for (int i = 0; i < 32; i++) f[i] = __uint_as_float(r[i]);
+#pragma unroll
+          for (int g = 0; g < 4; g++) *reinterpret_cast<uint4*>(dkrow + c * 32 + g * 8) = pack8(f + g * 8);
+        }
+        tmem_ld32(lane_addr + C::COL_DV + half * DH + c * 32, r);
+        tmem_ld_wait();
+        if (key < p.Sk) {
+#pragma unroll
+          for (int i = 0; i < 32; i++) f[i] = __uint_as_float(r[i]);
+#pragma unroll
+          for (int g = 0; g < 4; g++) *reinterpret_cast<uint4*>(dvrow + c * 32 + g * 8) = pack8(f + g * 8);
+        }
+      }
+    } else if (total_it == 0) {
+      // no query sees these keys: their gradients are zero
+      const int key = n0 + rit;
+      if (key < p.Sk) {
+        bf16* dkrow = p.dk + ((long long)b * p.Sk + key) * p.dk_ts + (long long)hk * D + half * DH;
+        bf16* dvrow = p.dv + ((long long)b * p.Sk + key) * p.dv_ts + (long long)hk * D + half * DH;
+        for (int c = 0; c < DH / 8; c++) {
+          *reinterpret_cast<uint4*>(dkrow + c * 8) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(dvrow + c * 8) = make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+    if (!ok && lane == 0) atomicExch(&g_fab_status[0], 3u);
+  }
+
+  fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D>
+int launch_fa_bwd(const void* q, const void* k, const void* v, const FaBwdParams& p, long long q_ts, long long k_ts,
+                  long long v_ts, cudaStream_t s) {
+  using C = BwdCfg<D>;
+  CUtensorMap tq, tk, tv, tdo;
+  int rc;
+  if ((rc = make_map_bf16(&tq, q, (uint64_t)p.hq * D, (uint64_t)p.B * p.Sq, (uint64_t)q_ts, 64, 128))) return rc;
+  if ((rc = make_map_bf16(&tk, k, (uint64_t)p.hkv * D, (uint64_t)p.B * p.Sk, (uint64_t)k_ts, 64, 128))) return rc;
+  if ((rc = make_map_bf16(&tv, v, (uint64_t)p.hkv * D, (uint64_t)p.B * p.Sk, (uint64_t)v_ts, 64, 128))) return rc;
+  if ((rc = make_map_bf16(&tdo, p.dout, (uint64_t)p.hq * D, (uint64_t)p.B * p.Sq, (uint64_t)p.do_ts, 64, 128))) return rc;
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(fa_bwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+    attr = true;
+  }
+  const long long rows = (long long)p.B * p.Sq * p.hq;
+  int dblocks = (int)((rows + 7) / 8 > 148 * 8 ? 148 * 8 : (rows + 7) / 8);
+  fa_delta_kernel<D><<<dblocks, 256, 0, s>>>(p);
+  LB_CHECK_LAUNCH();
+  dim3 grid((p.Sk + 127) / 128, p.hkv, p.B);
+  fa_bwd_tc_kernel<D><<<grid, 320, C::SMEM, s>>>(tq, tk, tv, tdo, p);
+  LB_CHECK_LAUNCH();
+  const long long total = rows * (D / 8);
+  int cblocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+  fa_dq_convert_kernel<D><<<cblocks, 256, 0, s>>>(p);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}
+
+}  // namespace
+
+// Copies the status words of the tcgen05 attention backward kernel to host memory and clears them.
+extern "C" int lb_flash_bwd_status(void* out) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_fab_status, sizeof(unsigned int) * 4);
+  if (e != cudaSuccess) { g_lb_last_cuda_error = (int)e; return LB_ERR_LAUNCH; }
+  unsigned int zeros[4] = {0, 0, 0, 0};
+  cudaMemcpyToSymbol(g_fab_status, zeros, sizeof(zeros));
+  return LB_OK;
+}
+
+// Same contract as lb_flash_bwd (flash_attn.cu): dq_acc is zero-initialised fp32 scratch
+// [B, Sq, hq, d], delta is fp32 scratch [B, hq, Sq].  head_dim 64 or 128; causal needs Sk >= Sq.
+extern "C" int lb_flash_bwd_tc(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                               const void* lse, void* delta, void* dq_acc, void* dq, void* dk, void* dv, int B, int Sq,
+                               int Sk, int hq, int hkv, int d, long long q_ts, long long k_ts, long long v_ts,
+                               long long o_ts, long long do_ts, long long dq_ts, long long dk_ts, long long dv_ts,
+                               float scale, int causal, void* stream) {
+  if (B <= 0 || Sq <= 0 || Sk <= 0 || hq % hkv) return LB_ERR_SHAPE;
+  if ((q_ts | k_ts | v_ts | o_ts | do_ts | dq_ts | dk_ts | dv_ts) % 8) return LB_ERR_SHAPE;
+  if (causal && Sk < Sq) return LB_ERR_SHAPE;
+  if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)dout | (uintptr_t)dq | (uintptr_t)dk | (uintptr_t)dv) & 15)
+    return LB_ERR_ARG;
+  FaBwdParams p{(const bf16*)o, (const bf16*)dout, (const float*)lse, (float*)delta, (float*)dq_acc,
+                (bf16*)dq, (bf16*)dk, (bf16*)dv, B, Sq, Sk, hq, hkv, o_ts, do_ts, dq_ts, dk_ts, dv_ts, scale, causal};
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (d) {
+    case 64: return launch_fa_bwd<64>(q, k, v, p, q_ts, k_ts, v_ts, s);
+    case 128: return launch_fa_bwd<128>(q, k, v, p, q_ts, k_ts, v_ts, s);
+    default: return LB_ERR_SHAPE;
+  }
+}

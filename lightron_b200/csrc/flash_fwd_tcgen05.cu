@@ -1,0 +1,360 @@
+// FlashAttention forward on the 5th-generation tensor cores (sm_100a), head_dim 64 or 128.
+//
+// One CTA owns 256 consecutive queries of one (batch, head): two 128-row tiles that ping-pong on
+// the tensor pipe.  Per 128-key block:
+//     S_t = Q_t K^T          tcgen05.mma, 128x128xd, operands in 128B-swizzled smem (TMA), D in TMEM
+//     softmax(S_t)           one thread per query row reads its row straight from TMEM
+//                            (tcgen05.ld), so max / sum need no shuffles; P_t goes to smem as bf16
+//     O_t (+)= P_t V         tcgen05.mma, 128 x d x 128, V is the MN-major B operand as it sits in memory
+// O_t stays in TMEM for the whole key loop; when a row maximum grows the softmax threads rescale
+// it in place (tcgen05.ld / st) before the next P V is issued.
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-5
+// softmax of tile 0, warps 6-9 softmax of tile 1.  While one tile is in softmax the tensor pipe
+// works on the other.  Layout / masking conventions are those of flash_attn.cu.
+// All waits are bounded; on expiry a status word is set and the CTA drains and frees its TMEM.
+#include "tcgen05.cuh"
+
+static __device__ unsigned int g_fa_status[4] = {0, 0, 0, 0};
+
+namespace {
+using namespace bw;
+
+struct FaFwdParams {
+  bf16* o;
+  float* lse;
+  int B, Sq, Sk, hq, hkv;
+  long long o_ts;
+  float scale;
+  int causal;
+};
+
+template <int D>
+struct FaCfg {
+  static constexpr int BM = 128, BN = 128;
+  static constexpr int KS = 2;
+  static constexpr int VS = (D == 64) ? 2 : 1;
+  static constexpr int ATOMS = D / 64;
+  static constexpr int ATOM_BYTES = 128 * 128;          // 128 rows x 128 B
+  static constexpr int TILE_BYTES = ATOMS * ATOM_BYTES; // one Q / K / V tile
+  static constexpr int P_BYTES = 2 * ATOM_BYTES;        // 128 x 128 bf16
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + 2 * TILE_BYTES;
+  static constexpr int OFF_V = OFF_K + KS * TILE_BYTES;
+  static constexpr int OFF_P = OFF_V + VS * TILE_BYTES;
+  static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;
+  static constexpr int NBAR = 1 + 2 * KS + 2 * VS + 6;
+};
+
+template <int D>
+__global__ void __launch_bounds__(320, 1)
+fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                 const __grid_constant__ CUtensorMap tv, const FaFwdParams p) {
+  using C = FaCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NBAR);
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = smem_u32(bars);
+  // barrier map
+  const uint32_t q_full = bar0;
+  auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bar0 + 8u * (1 + C::KS + s); };
+  auto v_full = [&](int s) { return bar0 + 8u * (1 + 2 * C::KS + s); };
+  auto v_empty = [&](int s) { return bar0 + 8u * (1 + 2 * C::KS + C::VS + s); };
+  const uint32_t bar1 = bar0 + 8u * (1 + 2 * C::KS + 2 * C::VS);
+  auto s_full = [&](int t) { return bar1 + 8u * t; };
+  auto p_full = [&](int t) { return bar1 + 8u * (2 + t); };
+  auto pv_done = [&](int t) { return bar1 + 8u * (4 + t); };
+
+  const int mblk = gridDim.x - 1 - blockIdx.x;   // late (long) causal rows first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.hq / p.hkv);
+  const int m0 = mblk * 2 * C::BM;
+  const int off = p.Sk - p.Sq;
+  const int kv_blocks = (p.Sk + C::BN - 1) / C::BN;
+  int nb[2];
+#pragma unroll
+  for (int t = 0; t < 2; t++) {
+    const int r0 = m0 + t * C::BM;
+    int n = kv_blocks;
+    if (p.causal) n = min(n, (r0 + C::BM - 1 + off) / C::BN + 1);
+    nb[t] = (r0 < p.Sq) ? n : 0;
+  }
+  const int nb_max = max(nb[0], nb[1]);
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(q_full, 1);
+    for (int s = 0; s < C::KS; s++) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); }
+    for (int s = 0; s < C::VS; s++) { mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1); }
+    for (int t = 0; t < 2; t++) { mbar_init(s_full(t), 1); mbar_init(p_full(t), 128); mbar_init(pv_done(t), 1); }
+    mbar_init_fence();
+    prefetch_tmap(&tq); prefetch_tmap(&tk); prefetch_tmap(&tv);
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0 && nb_max > 0) {
+      mbar_expect_tx(q_full, 2 * C::TILE_BYTES);
+#pragma unroll
+      for (int t = 0; t < 2; t++)
+#pragma unroll
+        for (int a = 0; a < C::ATOMS; a++)
+          tma_load_2d(sbase + C::OFF_Q + t * C::TILE_BYTES + a * C::ATOM_BYTES, &tq, h * D + a * 64,
+                      b * p.Sq + m0 + t * C::BM, q_full);
+      bool ok = true;
+      for (int j = 0; j < nb_max && ok; j++) {
+        const int ks = j % C::KS, vs = j % C::VS;
+        if (!mbar_wait(k_empty(ks), (((uint32_t)(j / C::KS)) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(k_full(ks), C::TILE_BYTES);
+#pragma unroll
+        for (int a = 0; a < C::ATOMS; a++)
+          tma_load_2d(sbase + C::OFF_K + ks * C::TILE_BYTES + a * C::ATOM_BYTES, &tk, hk * D + a * 64,
+                      b * p.Sk + j * C::BN, k_full(ks));
+        if (!mbar_wait(v_empty(vs), (((uint32_t)(j / C::VS)) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(v_full(vs), C::TILE_BYTES);
+#pragma unroll
+        for (int a = 0; a < C::ATOMS; a++)
+          tma_load_2d(sbase + C::OFF_V + vs * C::TILE_BYTES + a * C::ATOM_BYTES, &tv, hk * D + a * 64,
+                      b * p.Sk + j * C::BN, v_full(vs));
+      }
+      if (!ok) atomicExch(&g_fa_status[0], 1u);
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0 && nb_max > 0) {
+      const uint32_t idesc_s = make_idesc(C::BM, C::BN, 0, 0);
+      const uint32_t idesc_o = make_idesc(C::BM, D, 0, 1);
+      auto issue_s = [&](int t, int ks) {
+        const uint32_t qa = sbase + C::OFF_Q + t * C::TILE_BYTES;
+        const uint32_t ka = sbase + C::OFF_K + ks * C::TILE_BYTES;
+#pragma unroll
+        for (int s = 0; s < D / 16; s++) {
+          const uint32_t o = (s >> 2) * C::ATOM_BYTES + (s & 3) * 32;
+          umma_bf16(tmem_base + t * C::BN, make_desc(qa + o, 16, 1024), make_desc(ka + o, 16, 1024), idesc_s, s ? 1u : 0u);
+        }
+        umma_commit(s_full(t));
+      };
+      auto issue_pv = [&](int t, int vs, int j) {
+        const uint32_t pa = sbase + C::OFF_P + t * C::P_BYTES;
+        const uint32_t va = sbase + C::OFF_V + vs * C::TILE_BYTES;
+#pragma unroll
+        for (int s = 0; s < C::BN / 16; s++) {
+          const uint32_t ao = (s >> 2) * C::ATOM_BYTES + (s & 3) * 32;
+          umma_bf16(tmem_base + 2 * C::BN + t * D, make_desc(pa + ao, 16, 1024),
+                    make_desc(va + s * 2048, C::ATOM_BYTES, 1024), idesc_o, (j | s) ? 1u : 0u);
+        }
+        umma_commit(pv_done(t));
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      if (ok) ok = mbar_wait(k_full(0), 0, abort_flag);
+      if (ok) {
+        fence_after();
+        if (nb[0] > 0) issue_s(0, 0);
+        if (nb[1] > 0) issue_s(1, 0);
+        umma_commit(k_empty(0));
+      }
+      for (int j = 0; j < nb_max && ok; j++) {
+        const int vs = j % C::VS;
+        const int ks1 = (j + 1) % C::KS;
+        if (!mbar_wait(v_full(vs), ((uint32_t)(j / C::VS)) & 1u, abort_flag)) { ok = false; break; }
+        fence_after();
+        if (j < nb[0]) {
+          if (!mbar_wait(p_full(0), (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
+          fence_after();
+          issue_pv(0, vs, j);
+        }
+        if (j + 1 < nb_max) {
+          if (!mbar_wait(k_full(ks1), ((uint32_t)((j + 1) / C::KS)) & 1u, abort_flag)) { ok = false; break; }
+          fence_after();
+          if (j + 1 < nb[0]) issue_s(0, ks1);
+        }
+        if (j < nb[1]) {
+          if (!mbar_wait(p_full(1), (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
+          fence_after();
+          issue_pv(1, vs, j);
+        }
+        umma_commit(v_empty(vs));
+        if (j + 1 < nb_max) {
+          if (j + 1 < nb[1]) issue_s(1, ks1);
+          umma_commit(k_empty(ks1));
+        }
+      }
+      if (!ok) atomicExch(&g_fa_status[0], 2u);
+    }
+  } else {
+    // ------------------------------- softmax warps -------------------------------
+    const int t = (warp - 2) >> 2;
+    const int quad = warp & 3;
+    const int rit = quad * 32 + lane;              // row inside the tile
+    const int row = m0 + t * C::BM + rit;          // query index inside the sequence
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t ts_addr = lane_addr + t * C::BN;
+    const uint32_t to_addr = lane_addr + 2 * C::BN + t * D;
+    uint8_t* sP = smem + C::OFF_P + t * C::P_BYTES;
+    const float sl2 = p.scale * 1.4426950408889634f;
+    float m_i = -INFINITY, l_i = 0.f;
+    bool ok = true;
+    const int n_my = nb[t];
+    for (int j = 0; j < n_my; j++) {
+      if (!mbar_wait(s_full(t), (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
+      fence_after();
+      const int c0 = j * C::BN;
+      const int warp_row0 = m0 + t * C::BM + quad * 32;
+      const bool need_mask = (c0 + C::BN > p.Sk) || (p.causal && (c0 + C::BN - 1 > warp_row0 + off));
+      const int lim = p.causal ? min(p.Sk - 1, row + off) : p.Sk - 1;   // last visible key of this row
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < C::BN / 32; c++) {
+        uint32_t r[32];
+        tmem_ld32(ts_addr + c * 32, r);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; i++) if (c0 + c * 32 + i <= lim) mx = fmaxf(mx, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      }
+      const float m_new = fmaxf(m_i, mx);
+      const float m_s = (m_new == -INFINITY) ? 0.f : m_new * sl2;
+      const float corr = (m_i == -INFINITY) ? 0.f : exp2f(m_i * sl2 - m_s);
+      if (j > 0) {
+        // previous P V finished: O is stable and the P buffer may be overwritten
+        if (!mbar_wait(pv_done(t), (uint32_t)(j - 1) & 1u, abort_flag)) { ok = false; break; }
+        fence_after();
+        if (__any_sync(0xffffffffu, m_new > m_i)) {
+#pragma unroll 1
+          for (int c = 0; c < D / 32; c++) {
+            uint32_t r[32];
+            tmem_ld32(to_addr + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+            tmem_st32(to_addr + c * 32, r);
+          }
+          tmem_st_wait();
+        }
+      }
+      // pass 2: P = exp2(s*scale - max), row sum, bf16 P into swizzled smem
+      float rs = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < C::BN / 32; c++) {
+        uint32_t r[32];
+        tmem_ld32(ts_addr + c * 32, r);
+        tmem_ld_wait();
+        float f[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          float e = exp2f(__uint_as_float(r[i]) * sl2 - m_s);
+          if (need_mask && (c0 + c * 32 + i > lim)) e = 0.f;
+          f[i] = e;
+          rs += e;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+          const int cc = c * 4 + g;                    // 16-byte chunk index inside the 128-key row
+          *reinterpret_cast<uint4*>(sP + (cc >> 3) * C::ATOM_BYTES + sw128_off(rit, cc & 7)) = pack8(f + g * 8);
+        }
+      }
+      l_i = l_i * corr + rs;
+      m_i = m_new;
+      fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(p_full(t));
+    }
+    if (ok && n_my > 0) {
+      if (!mbar_wait(pv_done(t), (uint32_t)(n_my - 1) & 1u, abort_flag)) ok = false;
+    }
+    if (ok && n_my > 0) {
+      fence_after();
+      const float inv = l_i > 0.f ? 1.f / l_i : 0.f;
+      bf16* orow = p.o + ((long long)b * p.Sq + row) * p.o_ts + (long long)h * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; c++) {
+        uint32_t r[32];
+        tmem_ld32(to_addr + c * 32, r);
+        tmem_ld_wait();
+        if (row < p.Sq) {
+          float f[32];
+#pragma unroll
+          for (int i = 0; i < 32; i++) f[i] = __uint_as_float(r[i]) * inv;
+#pragma unroll
+          for (int g = 0; g < 4; g++) *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = pack8(f + g * 8);
+        }
+      }
+      if (row < p.Sq)
+        p.lse[((long long)b * p.hq + h) * p.Sq + row] = (l_i > 0.f) ? m_i * p.scale + logf(l_i) : -INFINITY;
+    }
+    if (!ok && lane == 0) atomicExch(&g_fa_status[0], 3u);
+  }
+
+  fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D>
+int launch_fa_fwd(const void* q, const void* k, const void* v, const FaFwdParams& p, long long q_ts, long long k_ts,
+                  long long v_ts, cudaStream_t s) {
+  using C = FaCfg<D>;
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_map_bf16(&tq, q, (uint64_t)p.hq * D, (uint64_t)p.B * p.Sq, (uint64_t)q_ts, 64, 128))) return rc;
+  if ((rc = make_map_bf16(&tk, k, (uint64_t)p.hkv * D, (uint64_t)p.B * p.Sk, (uint64_t)k_ts, 64, 128))) return rc;
+  if ((rc = make_map_bf16(&tv, v, (uint64_t)p.hkv * D, (uint64_t)p.B * p.Sk, (uint64_t)v_ts, 64, 128))) return rc;
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(fa_fwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+    attr = true;
+  }
+  dim3 grid((p.Sq + 255) / 256, p.hq, p.B);
+  fa_fwd_tc_kernel<D><<<grid, 320, C::SMEM, s>>>(tq, tk, tv, p);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}
+
+}  // namespace
+
+// Copies the status words of the tcgen05 attention kernels to host memory and clears them.
+extern "C" int lb_flash_status(void* out) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_fa_status, sizeof(unsigned int) * 4);
+  if (e != cudaSuccess) { g_lb_last_cuda_error = (int)e; return LB_ERR_LAUNCH; }
+  unsigned int zeros[4] = {0, 0, 0, 0};
+  cudaMemcpyToSymbol(g_fa_status, zeros, sizeof(zeros));
+  return LB_OK;
+}
+
+// Same contract as lb_flash_fwd (flash_attn.cu); head_dim 64 or 128, all pointers 16-byte
+// aligned, token strides multiples of 8, causal needs Sk >= Sq.  Returns LB_ERR_SHAPE otherwise.
+extern "C" int lb_flash_fwd_tc(const void* q, const void* k, const void* v, void* o, void* lse, int B, int Sq, int Sk,
+                               int hq, int hkv, int d, long long q_ts, long long k_ts, long long v_ts, long long o_ts,
+                               float scale, int causal, void* stream) {
+  if (B <= 0 || Sq <= 0 || Sk <= 0 || hq % hkv) return LB_ERR_SHAPE;
+  if ((q_ts | k_ts | v_ts | o_ts) % 8) return LB_ERR_SHAPE;
+  if (causal && Sk < Sq) return LB_ERR_SHAPE;
+  if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o) & 15) return LB_ERR_ARG;
+  FaFwdParams p{(bf16*)o, (float*)lse, B, Sq, Sk, hq, hkv, o_ts, scale, causal};
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (d) {
+    case 64: return launch_fa_fwd<64>(q, k, v, p, q_ts, k_ts, v_ts, s);
+    case 128: return launch_fa_fwd<128>(q, k, v, p, q_ts, k_ts, v_ts, s);
+    default: return LB_ERR_SHAPE;
+  }
+}

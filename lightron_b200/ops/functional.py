@@ -10,6 +10,7 @@ and ``F.cross_entropy`` (trainer.py:52).
 from __future__ import annotations
 
 import math
+import os
 from typing import List, Optional, Sequence, Tuple
 
 import torch
@@ -289,7 +290,9 @@ def flash_fwd_native(q, k, v, causal: bool, scale: float):
     Sk, hkv = k.shape[1], k.shape[2]
     o = torch.empty(B, Sq, hq, d, dtype=q.dtype, device=q.device)
     lse = torch.empty(B, hq, Sq, dtype=torch.float32, device=q.device)
-    native.call("lb_flash_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+    # head_dim 64 / 128 run on the tcgen05 kernel; 32 (and causal with Sk < Sq) on the mma.sync one
+    use_tc = d in (64, 128) and not (causal and Sk < Sq) and os.environ.get("LIGHTRON_FA", "tc") == "tc"
+    native.call("lb_flash_fwd_tc" if use_tc else "lb_flash_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
                 B, Sq, Sk, hq, hkv, d, q.stride(1), k.stride(1), v.stride(1), o.stride(1), float(scale), int(causal),
                 native.stream_ptr())
     return o, lse
@@ -311,7 +314,8 @@ def flash_bwd_native(q, k, v, o, lse, do, causal: bool, scale: float, dq=None, d
         _check_attn_layout(t)
     delta = torch.empty(B, hq, Sq, dtype=torch.float32, device=q.device)
     dq_acc = torch.zeros(B, Sq, hq, d, dtype=torch.float32, device=q.device)
-    native.call("lb_flash_bwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+    use_tc = d in (64, 128) and not (causal and Sk < Sq) and os.environ.get("LIGHTRON_FA_BWD", "tc") == "tc"
+    native.call("lb_flash_bwd_tc" if use_tc else "lb_flash_bwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
                 delta.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                 B, Sq, Sk, hq, hkv, d, q.stride(1), k.stride(1), v.stride(1), o.stride(1), do.stride(1),
                 dq.stride(1), dk.stride(1), dv.stride(1), float(scale), int(causal), native.stream_ptr())

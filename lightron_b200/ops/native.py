@@ -44,6 +44,11 @@ _SIGNATURES = {
     "lb_add_inplace": [_P, _P, _L, _P],
     "lb_gemm_bf16": [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _I, _P],
     "lb_flash_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _P],
+    "lb_flash_fwd_tc": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _P],
+    "lb_flash_status": [_P],
+    "lb_flash_bwd_status": [_P],
+    "lb_flash_bwd_tc": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
+                        _L, _L, _L, _L, _L, _L, _L, _L, _F, _I, _P],
     "lb_flash_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
                      _L, _L, _L, _L, _L, _L, _L, _L, _F, _I, _P],
 }
