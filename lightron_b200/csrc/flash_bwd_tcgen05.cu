@@ -8,16 +8,20 @@
 //     dK += dS^T Q           [128 k x d]       A = dS MN-major, B = Q MN-major
 //     dQ  = dS K             [128 q x d]       A = dS K-major,  B = K MN-major
 // S, dP, dQ, dV, dK live in TMEM (dV / dK accumulate there across the whole loop, so no
-// rescaling is ever needed).  256 "softmax" threads (8 warps; thread = one query row x half of
+// rescaling is ever needed).  512 math threads (16 warps; thread = one query row x a quarter of
 // the columns) read S and dP with tcgen05.ld, form P = exp(scale S - lse) and
 // dS = P (dP - delta) scale in registers, and write both as bf16 into 128B-swizzled shared
 // memory, where the same bytes serve as K-major (dQ) and MN-major (dV, dK) MMA operands.
-// dQ tiles are added to an fp32 accumulator in global memory with vector atomics.
-// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-9 math.
+// Each dQ tile goes TMEM -> registers -> a per-warp staging area -> one asynchronous bulk
+// reduce-add (cp.reduce.async.bulk .add.f32) per warp into an fp32 accumulator in global memory
+// whose layout is the staging layout (un-permuted by the final convert kernel), so no atomic
+// instructions pass through the load/store pipe.
+// Warp roles (576 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-17 math.
 // With head_dim 128 the dQ tile aliases the dP columns (TMEM is 512 columns) and Q/dO are
 // single-buffered; with head_dim 64 Q/dO are double-buffered and S/dP of the next query block
 // are issued while the current one is still in the math warps.
 // All waits are bounded; on expiry a status word is set and the CTA drains and frees its TMEM.
+#include <stdlib.h>
 #include "tcgen05.cuh"
 
 static __device__ unsigned int g_fab_status[4] = {0, 0, 0, 0};
@@ -34,6 +38,7 @@ struct FaBwdParams {
   long long o_ts, do_ts, dq_ts, dk_ts, dv_ts;
   float scale;
   int causal;
+  int debug;
 };
 
 template <int D>
@@ -45,21 +50,59 @@ struct BwdCfg {
   static constexpr int ATOM_BYTES = 128 * 128;
   static constexpr int TILE_BYTES = ATOMS * ATOM_BYTES;
   static constexpr int P_BYTES = 2 * ATOM_BYTES;
+  static constexpr int DQC = D / 4;                     // dQ / dK / dV columns per math thread
+  static constexpr int STG_WARP = 32 * DQC * 4;         // bytes of dQ staging per warp
+  static constexpr int STG_BYTES = 16 * STG_WARP;       // 32 KiB (d = 64) or 64 KiB (d = 128)
+  static constexpr bool STG_ALIAS = (D == 128);         // staging shares the P/dS bytes when smem is short
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + TILE_BYTES;
   static constexpr int OFF_Q = OFF_V + TILE_BYTES;              // [ST]
   static constexpr int OFF_DO = OFF_Q + ST * TILE_BYTES;        // [ST]
   static constexpr int OFF_P = OFF_DO + ST * TILE_BYTES;
   static constexpr int OFF_DS = OFF_P + P_BYTES;
-  static constexpr int OFF_BAR = OFF_DS + P_BYTES;
+  static constexpr int OFF_STG = STG_ALIAS ? OFF_P : OFF_DS + P_BYTES;
+  static constexpr int OFF_BAR = STG_ALIAS ? OFF_DS + P_BYTES : OFF_STG + STG_BYTES;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
-  static constexpr int NBAR = 1 + 2 * ST + 5;
+  static constexpr int NBAR = 1 + 2 * ST + 6;
+  static constexpr int NTHREADS = 576;
   // TMEM columns
   static constexpr int COL_S = 0, COL_DP = 128;
   static constexpr int COL_DQ = (D == 64) ? 256 : 128;          // aliases dP for d = 128
   static constexpr int COL_DV = (D == 64) ? 320 : 256;
-  static constexpr int COL_DK = (D == 64) ? 384 : 384;
+  static constexpr int COL_DK = 384;
+  // Swizzle of the 16-byte chunks of one thread's dQ row segment inside its warp's staging area
+  // (keeps the 16-byte shared-memory stores of a warp conflict-free).
+  __host__ __device__ static constexpr int stg_chunk(int c, int lane) {
+    return (D == 64) ? (c ^ ((lane >> 1) & 3)) : (c ^ (lane & 7));
+  }
 };
+
+// fp32 dQ accumulator layout: tile (b, h, mblock) -> 16 warp slots (part * 4 + quad) -> 32 lanes ->
+// D/4 floats in swizzled 16-byte chunks.  Element (row r of the tile, column col):
+//   quad = r / 32, lane = r % 32, part = col / (D/4), chunk = (col % (D/4)) / 4.
+template <int D>
+__global__ void fa_dq_convert_kernel(const FaBwdParams p) {
+  using C = BwdCfg<D>;
+  constexpr int VPR = D / 8;
+  const int n_mblocks = (p.Sq + 127) / 128;
+  const long long total = (long long)p.B * p.Sq * p.hq * VPR;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(idx % VPR);
+    const long long th = idx / VPR;
+    const int h = (int)(th % p.hq);
+    const long long bi = th / p.hq;
+    const int b = (int)(bi / p.Sq), row = (int)(bi % p.Sq);
+    const int mblock = row >> 7, r = row & 127, quad = r >> 5, lane = r & 31;
+    const int col0 = v * 8, part = col0 / C::DQC, c0 = (col0 % C::DQC) >> 2;
+    const float* tile = p.dq_acc + (((long long)b * p.hq + h) * n_mblocks + mblock) * (128 * D) +
+                        (long long)(part * 4 + quad) * (32 * C::DQC) + lane * C::DQC;
+    const float4 a = *reinterpret_cast<const float4*>(tile + C::stg_chunk(c0, lane) * 4);
+    const float4 c = *reinterpret_cast<const float4*>(tile + C::stg_chunk(c0 + 1, lane) * 4);
+    const float f[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
+    *reinterpret_cast<uint4*>(p.dq + bi * p.dq_ts + (long long)h * D + v * 8) = pack8(f);
+  }
+}
 
 template <int D>
 __global__ void fa_delta_kernel(const FaBwdParams p) {
@@ -86,24 +129,7 @@ __global__ void fa_delta_kernel(const FaBwdParams p) {
 }
 
 template <int D>
-__global__ void fa_dq_convert_kernel(const FaBwdParams p) {
-  constexpr int VPR = D / 8;
-  const long long total = (long long)p.B * p.Sq * p.hq * VPR;
-  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += (long long)gridDim.x * blockDim.x) {
-    const int v = (int)(idx % VPR);
-    const long long th = idx / VPR;
-    const int h = (int)(th % p.hq);
-    const long long bi = th / p.hq;
-    const float4* src = reinterpret_cast<const float4*>(p.dq_acc + (bi * p.hq + h) * D + v * 8);
-    const float4 a = src[0], c = src[1];
-    const float f[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
-    *reinterpret_cast<uint4*>(p.dq + bi * p.dq_ts + (long long)h * D + v * 8) = pack8(f);
-  }
-}
-
-template <int D>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(576, 1)
 fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                  const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo, const FaBwdParams p) {
   using C = BwdCfg<D>;
@@ -120,7 +146,8 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   auto qdo_full = [&](int s) { return bar0 + 8u * (1 + s); };
   auto qdo_empty = [&](int s) { return bar0 + 8u * (1 + C::ST + s); };
   const uint32_t bar1 = bar0 + 8u * (1 + 2 * C::ST);
-  const uint32_t sdp_full = bar1, sdp_free = bar1 + 8, pds_full = bar1 + 16, dq_full = bar1 + 24, dq_free = bar1 + 32;
+  const uint32_t sdp_full = bar1, sdp_free = bar1 + 8, pds_full = bar1 + 16, dq_full = bar1 + 24, dq_free = bar1 + 32,
+                 stg_free = bar1 + 40;
 
   const int nblk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int n0 = nblk * C::BN;
@@ -140,10 +167,11 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     mbar_init(kv_full, 1);
     for (int s = 0; s < C::ST; s++) { mbar_init(qdo_full(s), 1); mbar_init(qdo_empty(s), 1); }
     mbar_init(sdp_full, 1);
-    mbar_init(sdp_free, 256);
-    mbar_init(pds_full, 256);
+    mbar_init(sdp_free, 512);
+    mbar_init(pds_full, 512);
     mbar_init(dq_full, 1);
-    mbar_init(dq_free, 256);
+    mbar_init(dq_free, 512);
+    mbar_init(stg_free, 16);
     mbar_init_fence();
     prefetch_tmap(&tq); prefetch_tmap(&tk); prefetch_tmap(&tv); prefetch_tmap(&tdo);
   }
@@ -184,35 +212,42 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       const uint32_t idesc_s = make_idesc(128, 128, 0, 0);     // S, dP: K-major A and B
       const uint32_t idesc_kv = make_idesc(128, D, 1, 1);      // dV, dK: MN-major A and B
       const uint32_t idesc_dq = make_idesc(128, D, 0, 1);      // dQ: K-major A, MN-major B
-      const uint32_t sK = sbase + C::OFF_K, sV = sbase + C::OFF_V, sP = sbase + C::OFF_P, sDS = sbase + C::OFF_DS;
+      // descriptor bases; a stage / k-step only changes the 16-byte-granular start address
+      const uint64_t kK = make_desc(sbase + C::OFF_K, 16, 1024), kV = make_desc(sbase + C::OFF_V, 16, 1024);
+      const uint64_t kQ = make_desc(sbase + C::OFF_Q, 16, 1024), kDO = make_desc(sbase + C::OFF_DO, 16, 1024);
+      const uint64_t kDS = make_desc(sbase + C::OFF_DS, 16, 1024);
+      const uint64_t mK = make_desc(sbase + C::OFF_K, C::ATOM_BYTES, 1024);
+      const uint64_t mQ = make_desc(sbase + C::OFF_Q, C::ATOM_BYTES, 1024), mDO = make_desc(sbase + C::OFF_DO, C::ATOM_BYTES, 1024);
+      const uint64_t mP = make_desc(sbase + C::OFF_P, C::ATOM_BYTES, 1024), mDS = make_desc(sbase + C::OFF_DS, C::ATOM_BYTES, 1024);
       auto issue_s_dp = [&](int st) {
-        const uint32_t sQ = sbase + C::OFF_Q + st * C::TILE_BYTES, sDO = sbase + C::OFF_DO + st * C::TILE_BYTES;
+        const uint64_t so = (uint64_t)((st * C::TILE_BYTES) >> 4);
 #pragma unroll
         for (int s = 0; s < D / 16; s++) {
-          const uint32_t o = (s >> 2) * C::ATOM_BYTES + (s & 3) * 32;
-          umma_bf16(tmem_base + C::COL_S, make_desc(sQ + o, 16, 1024), make_desc(sK + o, 16, 1024), idesc_s, s ? 1u : 0u);
+          const uint64_t o = (uint64_t)(((s >> 2) * C::ATOM_BYTES + (s & 3) * 32) >> 4);
+          umma_bf16(tmem_base + C::COL_S, kQ + so + o, kK + o, idesc_s, s ? 1u : 0u);
         }
 #pragma unroll
         for (int s = 0; s < D / 16; s++) {
-          const uint32_t o = (s >> 2) * C::ATOM_BYTES + (s & 3) * 32;
-          umma_bf16(tmem_base + C::COL_DP, make_desc(sDO + o, 16, 1024), make_desc(sV + o, 16, 1024), idesc_s, s ? 1u : 0u);
+          const uint64_t o = (uint64_t)(((s >> 2) * C::ATOM_BYTES + (s & 3) * 32) >> 4);
+          umma_bf16(tmem_base + C::COL_DP, kDO + so + o, kV + o, idesc_s, s ? 1u : 0u);
         }
         umma_commit(sdp_full);
       };
       auto issue_grads = [&](int st, int it) {
-        const uint32_t sQ = sbase + C::OFF_Q + st * C::TILE_BYTES, sDO = sbase + C::OFF_DO + st * C::TILE_BYTES;
+        const uint64_t so = (uint64_t)((st * C::TILE_BYTES) >> 4);
+        const uint32_t acc0 = it ? 1u : 0u;
+        umma_bf16(tmem_base + C::COL_DV, mP, mDO + so, idesc_kv, acc0);       // dV += P^T dO   (K = 128 queries)
 #pragma unroll
-        for (int s = 0; s < C::BM / 16; s++)      // dV += P^T dO   (K = 128 queries)
-          umma_bf16(tmem_base + C::COL_DV, make_desc(sP + s * 2048, C::ATOM_BYTES, 1024),
-                    make_desc(sDO + s * 2048, C::ATOM_BYTES, 1024), idesc_kv, (it | s) ? 1u : 0u);
+        for (int s = 1; s < C::BM / 16; s++)
+          umma_bf16(tmem_base + C::COL_DV, mP + (uint64_t)(s * 128), mDO + so + (uint64_t)(s * 128), idesc_kv, 1u);
+        umma_bf16(tmem_base + C::COL_DK, mDS, mQ + so, idesc_kv, acc0);       // dK += dS^T Q
 #pragma unroll
-        for (int s = 0; s < C::BM / 16; s++)      // dK += dS^T Q
-          umma_bf16(tmem_base + C::COL_DK, make_desc(sDS + s * 2048, C::ATOM_BYTES, 1024),
-                    make_desc(sQ + s * 2048, C::ATOM_BYTES, 1024), idesc_kv, (it | s) ? 1u : 0u);
+        for (int s = 1; s < C::BM / 16; s++)
+          umma_bf16(tmem_base + C::COL_DK, mDS + (uint64_t)(s * 128), mQ + so + (uint64_t)(s * 128), idesc_kv, 1u);
 #pragma unroll
-        for (int s = 0; s < C::BN / 16; s++)      // dQ = dS K      (K = 128 keys)
-          umma_bf16(tmem_base + C::COL_DQ, make_desc(sDS + (s >> 2) * C::ATOM_BYTES + (s & 3) * 32, 16, 1024),
-                    make_desc(sK + s * 2048, C::ATOM_BYTES, 1024), idesc_dq, s ? 1u : 0u);
+        for (int s = 0; s < C::BN / 16; s++)                                   // dQ = dS K      (K = 128 keys)
+          umma_bf16(tmem_base + C::COL_DQ, kDS + (uint64_t)(((s >> 2) * C::ATOM_BYTES + (s & 3) * 32) >> 4),
+                    mK + (uint64_t)(s * 128), idesc_dq, s ? 1u : 0u);
         umma_commit(dq_full);
         umma_commit(qdo_empty(st));
       };
@@ -248,36 +283,49 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   } else {
     // ------------------------------- math warps -------------------------------
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;               // which 64 of the 128 key columns / which half of d
+    const int part = (warp - 2) >> 2;               // which 32 of the 128 key columns / which quarter of d
     const int rit = quad * 32 + lane;               // row inside the 128-row tile
+    const int ws = part * 4 + quad;                 // this warp's slot in the dQ staging / accumulator layout
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     const float sl2 = p.scale * 1.4426950408889634f;
     const float l2e = 1.4426950408889634f;
-    uint8_t* sPh = smem + C::OFF_P + half * C::ATOM_BYTES;
-    uint8_t* sDSh = smem + C::OFF_DS + half * C::ATOM_BYTES;
-    constexpr int DH = D / 2;                        // dQ / dK / dV columns per thread
+    uint8_t* sProw = smem + C::OFF_P + (part >> 1) * C::ATOM_BYTES;
+    uint8_t* sDSrow = smem + C::OFF_DS + (part >> 1) * C::ATOM_BYTES;
+    uint8_t* stg = smem + C::OFF_STG + ws * C::STG_WARP;
+    constexpr int DQC = C::DQC;
     bool ok = true;
-    int prev_row = 0, prev_h = 0;
+    int prev_m0 = 0, prev_h = 0;
+    int n_flushed = 0;
     auto flush_dq = [&](int it_prev) -> bool {
-      // dQ of the previous query block: TMEM -> fp32 atomics
+      // dQ of query block `it_prev`: TMEM -> registers -> staging -> bulk reduce-add to global
       if (!mbar_wait(dq_full, (uint32_t)it_prev & 1u, abort_flag)) return false;
       fence_after();
-      float* dst = p.dq_acc + (((long long)b * p.Sq + prev_row) * p.hq + prev_h) * D + half * DH;
-#pragma unroll 1
-      for (int c = 0; c < DH / 32; c++) {
-        uint32_t r[32];
-        tmem_ld32(lane_addr + C::COL_DQ + half * DH + c * 32, r);
-        tmem_ld_wait();
-        if (prev_row < p.Sq) {
-#pragma unroll
-          for (int g = 0; g < 8; g++)
-            atomicAdd(reinterpret_cast<float4*>(dst + c * 32 + g * 4),
-                      make_float4(__uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]), __uint_as_float(r[g * 4 + 2]),
-                                  __uint_as_float(r[g * 4 + 3])));
-        }
-      }
+      uint32_t r[DQC];
+      tmem_ld<DQC>(lane_addr + C::COL_DQ + part * DQC, r);
+      tmem_ld_wait();
       fence_before();
       mbar_arrive(dq_free);
+      if (!C::STG_ALIAS) {
+        if (lane == 0) bulk_wait_read();            // this warp's previous bulk op has read the staging area
+        __syncwarp();
+      }
+#pragma unroll
+      for (int c = 0; c < DQC / 4; c++)
+        *reinterpret_cast<uint4*>(stg + lane * (DQC * 4) + C::stg_chunk(c, lane) * 16) =
+            make_uint4(r[c * 4], r[c * 4 + 1], r[c * 4 + 2], r[c * 4 + 3]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        float* dst = p.dq_acc + (((long long)b * p.hq + prev_h) * n_mblocks + (prev_m0 >> 7)) * (128 * D) +
+                     (long long)ws * (32 * DQC);
+        bulk_reduce_add_f32(dst, smem_u32(stg), C::STG_WARP);
+        bulk_commit();
+        if (C::STG_ALIAS) {                          // the bytes are P/dS again in the next block
+          bulk_wait_read();
+          mbar_arrive(stg_free);
+        }
+      }
+      n_flushed++;
       return true;
     };
     for (int it = 0; it < total_it; it++) {
@@ -292,30 +340,29 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       }
       if (!mbar_wait(sdp_full, (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
       fence_after();
-      uint32_t sr[64], dr[64];
-      tmem_ld32(lane_addr + C::COL_S + half * 64, sr);
-      tmem_ld32(lane_addr + C::COL_S + half * 64 + 32, sr + 32);
-      tmem_ld32(lane_addr + C::COL_DP + half * 64, dr);
-      tmem_ld32(lane_addr + C::COL_DP + half * 64 + 32, dr + 32);
+      uint32_t sr[32], dr[32];
+      tmem_ld32(lane_addr + C::COL_S + part * 32, sr);
+      tmem_ld32(lane_addr + C::COL_DP + part * 32, dr);
       tmem_ld_wait();
       fence_before();
       mbar_arrive(sdp_free);
-      // P and dS for this thread's 64 keys
-      const int key0 = n0 + half * 64;
+      // P and dS for this thread's 32 keys
+      const int key0 = n0 + part * 32;
       const bool need_mask = (n0 + C::BN > p.Sk) || (p.causal && (n0 + C::BN - 1 > m0 + quad * 32 + off));
-      const int lim = p.causal ? min(p.Sk - 1, row + off) : p.Sk - 1;
+      const int lim = (p.causal ? min(p.Sk - 1, row + off) : p.Sk - 1) - key0;
       const float nl = -lse_r * l2e;
-      uint32_t pp[32], dd[32];
+      const float nds = -delta_r * p.scale;
+      uint32_t pp[16], dd[16];
 #pragma unroll
-      for (int i = 0; i < 64; i += 2) {
+      for (int i = 0; i < 32; i += 2) {
         float p0 = exp2f(fmaf(__uint_as_float(sr[i]), sl2, nl));
         float p1 = exp2f(fmaf(__uint_as_float(sr[i + 1]), sl2, nl));
         if (need_mask) {
-          if (key0 + i > lim) p0 = 0.f;
-          if (key0 + i + 1 > lim) p1 = 0.f;
+          if (i > lim) p0 = 0.f;
+          if (i + 1 > lim) p1 = 0.f;
         }
-        const float d0 = p0 * (__uint_as_float(dr[i]) - delta_r) * p.scale;
-        const float d1 = p1 * (__uint_as_float(dr[i + 1]) - delta_r) * p.scale;
+        const float d0 = p0 * fmaf(__uint_as_float(dr[i]), p.scale, nds);
+        const float d1 = p1 * fmaf(__uint_as_float(dr[i + 1]), p.scale, nds);
         bf162 pb = __floats2bfloat162_rn(p0, p1), db = __floats2bfloat162_rn(d0, d1);
         pp[i >> 1] = *reinterpret_cast<uint32_t*>(&pb);
         dd[i >> 1] = *reinterpret_cast<uint32_t*>(&db);
@@ -325,54 +372,55 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       if (C::EARLY && it > 0) {
         if (!flush_dq(it - 1)) { ok = false; break; }
       }
+      if (C::STG_ALIAS && it > 0) {                  // every warp's bulk op has finished reading the shared bytes
+        if (!mbar_wait(stg_free, (uint32_t)(it - 1) & 1u, abort_flag)) { ok = false; break; }
+      }
 #pragma unroll
-      for (int c = 0; c < 8; c++) {
-        const uint32_t o = sw128_off(rit, c);
-        *reinterpret_cast<uint4*>(sPh + o) = make_uint4(pp[c * 4], pp[c * 4 + 1], pp[c * 4 + 2], pp[c * 4 + 3]);
-        *reinterpret_cast<uint4*>(sDSh + o) = make_uint4(dd[c * 4], dd[c * 4 + 1], dd[c * 4 + 2], dd[c * 4 + 3]);
+      for (int c = 0; c < 4; c++) {
+        const uint32_t o = sw128_off(rit, (part & 1) * 4 + c);
+        *reinterpret_cast<uint4*>(sProw + o) = make_uint4(pp[c * 4], pp[c * 4 + 1], pp[c * 4 + 2], pp[c * 4 + 3]);
+        *reinterpret_cast<uint4*>(sDSrow + o) = make_uint4(dd[c * 4], dd[c * 4 + 1], dd[c * 4 + 2], dd[c * 4 + 3]);
       }
       fence_proxy_async_smem();
       mbar_arrive(pds_full);
-      prev_row = row;
+      prev_m0 = m0;
       prev_h = h;
       if (!C::EARLY) {   // dQ aliases dP: it must be drained before the next S/dP can be issued
         if (!flush_dq(it)) { ok = false; break; }
       }
     }
     if (C::EARLY && ok && total_it > 0) ok = flush_dq(total_it - 1);
+    if (lane == 0 && n_flushed > 0) bulk_wait_read();   // staging must outlive the last bulk read
     if (ok && total_it > 0) {
       // dq_full of the last block was committed after every MMA: dV and dK are final
       const int key = n0 + rit;
-      bf16* dkrow = p.dk + ((long long)b * p.Sk + key) * p.dk_ts + (long long)hk * D + half * DH;
-      bf16* dvrow = p.dv + ((long long)b * p.Sk + key) * p.dv_ts + (long long)hk * D + half * DH;
-#pragma unroll 1
-      for (int c = 0; c < DH / 32; c++) {
-        uint32_t r[32];
-        float f[32];
-        tmem_ld32(lane_addr + C::COL_DK + half * DH + c * 32, r);
-        tmem_ld_wait();
-        if (key < p.Sk) {
+      bf16* dkrow = p.dk + ((long long)b * p.Sk + key) * p.dk_ts + (long long)hk * D + part * DQC;
+      bf16* dvrow = p.dv + ((long long)b * p.Sk + key) * p.dv_ts + (long long)hk * D + part * DQC;
+      uint32_t r[DQC];
+      float f[DQC];
+      tmem_ld<DQC>(lane_addr + C::COL_DK + part * DQC, r);
+      tmem_ld_wait();
+      if (key < p.Sk) {
 #pragma unroll
-          for (int i = 0; i < 32; i++) f[i] = __uint_as_float(r[i]);
+        for (int i = 0; i < DQC; i++) f[i] = __uint_as_float(r[i]);
 #pragma unroll
-          for (int g = 0; g < 4; g++) *reinterpret_cast<uint4*>(dkrow + c * 32 + g * 8) = pack8(f + g * 8);
-        }
-        tmem_ld32(lane_addr + C::COL_DV + half * DH + c * 32, r);
-        tmem_ld_wait();
-        if (key < p.Sk) {
+        for (int g = 0; g < DQC / 8; g++) *reinterpret_cast<uint4*>(dkrow + g * 8) = pack8(f + g * 8);
+      }
+      tmem_ld<DQC>(lane_addr + C::COL_DV + part * DQC, r);
+      tmem_ld_wait();
+      if (key < p.Sk) {
 #pragma unroll
-          for (int i = 0; i < 32; i++) f[i] = __uint_as_float(r[i]);
+        for (int i = 0; i < DQC; i++) f[i] = __uint_as_float(r[i]);
 #pragma unroll
-          for (int g = 0; g < 4; g++) *reinterpret_cast<uint4*>(dvrow + c * 32 + g * 8) = pack8(f + g * 8);
-        }
+        for (int g = 0; g < DQC / 8; g++) *reinterpret_cast<uint4*>(dvrow + g * 8) = pack8(f + g * 8);
       }
     } else if (total_it == 0) {
       // no query sees these keys: their gradients are zero
       const int key = n0 + rit;
       if (key < p.Sk) {
-        bf16* dkrow = p.dk + ((long long)b * p.Sk + key) * p.dk_ts + (long long)hk * D + half * DH;
-        bf16* dvrow = p.dv + ((long long)b * p.Sk + key) * p.dv_ts + (long long)hk * D + half * DH;
-        for (int c = 0; c < DH / 8; c++) {
+        bf16* dkrow = p.dk + ((long long)b * p.Sk + key) * p.dk_ts + (long long)hk * D + part * DQC;
+        bf16* dvrow = p.dv + ((long long)b * p.Sk + key) * p.dv_ts + (long long)hk * D + part * DQC;
+        for (int c = 0; c < DQC / 8; c++) {
           *reinterpret_cast<uint4*>(dkrow + c * 8) = make_uint4(0, 0, 0, 0);
           *reinterpret_cast<uint4*>(dvrow + c * 8) = make_uint4(0, 0, 0, 0);
         }
@@ -409,7 +457,7 @@ int launch_fa_bwd(const void* q, const void* k, const void* v, const FaBwdParams
   fa_delta_kernel<D><<<dblocks, 256, 0, s>>>(p);
   LB_CHECK_LAUNCH();
   dim3 grid((p.Sk + 127) / 128, p.hkv, p.B);
-  fa_bwd_tc_kernel<D><<<grid, 320, C::SMEM, s>>>(tq, tk, tv, tdo, p);
+  fa_bwd_tc_kernel<D><<<grid, C::NTHREADS, C::SMEM, s>>>(tq, tk, tv, tdo, p);
   LB_CHECK_LAUNCH();
   const long long total = rows * (D / 8);
   int cblocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
@@ -429,8 +477,9 @@ extern "C" int lb_flash_bwd_status(void* out) {
   return LB_OK;
 }
 
-// Same contract as lb_flash_bwd (flash_attn.cu): dq_acc is zero-initialised fp32 scratch
-// [B, Sq, hq, d], delta is fp32 scratch [B, hq, Sq].  head_dim 64 or 128; causal needs Sk >= Sq.
+// Same contract as lb_flash_bwd (flash_attn.cu) except for the scratch: dq_acc is zero-initialised
+// fp32 of B * hq * ceil(Sq/128) * 128 * d elements (tile-permuted layout, see fa_dq_convert_kernel);
+// delta is fp32 scratch [B, hq, Sq].  head_dim 64 or 128; causal needs Sk >= Sq.
 extern "C" int lb_flash_bwd_tc(const void* q, const void* k, const void* v, const void* o, const void* dout,
                                const void* lse, void* delta, void* dq_acc, void* dq, void* dk, void* dv, int B, int Sq,
                                int Sk, int hq, int hkv, int d, long long q_ts, long long k_ts, long long v_ts,
@@ -442,7 +491,8 @@ extern "C" int lb_flash_bwd_tc(const void* q, const void* k, const void* v, cons
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)dout | (uintptr_t)dq | (uintptr_t)dk | (uintptr_t)dv) & 15)
     return LB_ERR_ARG;
   FaBwdParams p{(const bf16*)o, (const bf16*)dout, (const float*)lse, (float*)delta, (float*)dq_acc,
-                (bf16*)dq, (bf16*)dk, (bf16*)dv, B, Sq, Sk, hq, hkv, o_ts, do_ts, dq_ts, dk_ts, dv_ts, scale, causal};
+                (bf16*)dq, (bf16*)dk, (bf16*)dv, B, Sq, Sk, hq, hkv, o_ts, do_ts, dq_ts, dk_ts, dv_ts, scale, causal,
+                getenv("LB_FA_DEBUG") ? atoi(getenv("LB_FA_DEBUG")) : 0};
   cudaStream_t s = (cudaStream_t)stream;
   switch (d) {
     case 64: return launch_fa_bwd<64>(q, k, v, p, q_ts, k_ts, v_ts, s);

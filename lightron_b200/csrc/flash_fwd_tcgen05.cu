@@ -43,7 +43,7 @@ struct FaCfg {
   static constexpr int OFF_P = OFF_V + VS * TILE_BYTES;
   static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
-  static constexpr int NBAR = 1 + 2 * KS + 2 * VS + 6;
+  static constexpr int NBAR = 1 + 2 * KS + 2 * VS + 8;
 };
 
 template <int D>
@@ -70,6 +70,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   auto s_full = [&](int t) { return bar1 + 8u * t; };
   auto p_full = [&](int t) { return bar1 + 8u * (2 + t); };
   auto pv_done = [&](int t) { return bar1 + 8u * (4 + t); };
+  auto s_free = [&](int t) { return bar1 + 8u * (6 + t); };
 
   const int mblk = gridDim.x - 1 - blockIdx.x;   // late (long) causal rows first
   const int h = blockIdx.y, b = blockIdx.z;
@@ -92,7 +93,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     mbar_init(q_full, 1);
     for (int s = 0; s < C::KS; s++) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); }
     for (int s = 0; s < C::VS; s++) { mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1); }
-    for (int t = 0; t < 2; t++) { mbar_init(s_full(t), 1); mbar_init(p_full(t), 128); mbar_init(pv_done(t), 1); }
+    for (int t = 0; t < 2; t++) { mbar_init(s_full(t), 1); mbar_init(p_full(t), 128); mbar_init(pv_done(t), 1); mbar_init(s_free(t), 128); }
     mbar_init_fence();
     prefetch_tmap(&tq); prefetch_tmap(&tk); prefetch_tmap(&tv);
   }
@@ -136,59 +137,76 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     if (lane == 0 && nb_max > 0) {
       const uint32_t idesc_s = make_idesc(C::BM, C::BN, 0, 0);
       const uint32_t idesc_o = make_idesc(C::BM, D, 0, 1);
+      // descriptor bases; a tile / stage / k-step only changes the 16-byte-granular start address
+      const uint64_t dq0 = make_desc(sbase + C::OFF_Q, 16, 1024);
+      const uint64_t dk0 = make_desc(sbase + C::OFF_K, 16, 1024);
+      const uint64_t dp0 = make_desc(sbase + C::OFF_P, 16, 1024);
+      const uint64_t dv0 = make_desc(sbase + C::OFF_V, C::ATOM_BYTES, 1024);
       auto issue_s = [&](int t, int ks) {
-        const uint32_t qa = sbase + C::OFF_Q + t * C::TILE_BYTES;
-        const uint32_t ka = sbase + C::OFF_K + ks * C::TILE_BYTES;
+        const uint64_t qa = dq0 + (uint64_t)((t * C::TILE_BYTES) >> 4);
+        const uint64_t ka = dk0 + (uint64_t)((ks * C::TILE_BYTES) >> 4);
+        const uint32_t dst = tmem_base + t * C::BN;
 #pragma unroll
         for (int s = 0; s < D / 16; s++) {
-          const uint32_t o = (s >> 2) * C::ATOM_BYTES + (s & 3) * 32;
-          umma_bf16(tmem_base + t * C::BN, make_desc(qa + o, 16, 1024), make_desc(ka + o, 16, 1024), idesc_s, s ? 1u : 0u);
+          const uint64_t o = (uint64_t)(((s >> 2) * C::ATOM_BYTES + (s & 3) * 32) >> 4);
+          umma_bf16(dst, qa + o, ka + o, idesc_s, s ? 1u : 0u);
         }
         umma_commit(s_full(t));
       };
       auto issue_pv = [&](int t, int vs, int j) {
-        const uint32_t pa = sbase + C::OFF_P + t * C::P_BYTES;
-        const uint32_t va = sbase + C::OFF_V + vs * C::TILE_BYTES;
+        const uint64_t pa = dp0 + (uint64_t)((t * C::P_BYTES) >> 4);
+        const uint64_t va = dv0 + (uint64_t)((vs * C::TILE_BYTES) >> 4);
+        const uint32_t dst = tmem_base + 2 * C::BN + t * D;
+        umma_bf16(dst, pa, va, idesc_o, j ? 1u : 0u);
 #pragma unroll
-        for (int s = 0; s < C::BN / 16; s++) {
-          const uint32_t ao = (s >> 2) * C::ATOM_BYTES + (s & 3) * 32;
-          umma_bf16(tmem_base + 2 * C::BN + t * D, make_desc(pa + ao, 16, 1024),
-                    make_desc(va + s * 2048, C::ATOM_BYTES, 1024), idesc_o, (j | s) ? 1u : 0u);
-        }
+        for (int s = 1; s < C::BN / 16; s++)
+          umma_bf16(dst, pa + (uint64_t)(((s >> 2) * C::ATOM_BYTES + (s & 3) * 32) >> 4), va + (uint64_t)((s * 2048) >> 4),
+                    idesc_o, 1u);
         umma_commit(pv_done(t));
       };
       bool ok = mbar_wait(q_full, 0, abort_flag);
-      if (ok) ok = mbar_wait(k_full(0), 0, abort_flag);
-      if (ok) {
-        fence_after();
-        if (nb[0] > 0) issue_s(0, 0);
-        if (nb[1] > 0) issue_s(1, 0);
-        umma_commit(k_empty(0));
-      }
-      for (int j = 0; j < nb_max && ok; j++) {
-        const int vs = j % C::VS;
-        const int ks1 = (j + 1) % C::KS;
-        if (!mbar_wait(v_full(vs), ((uint32_t)(j / C::VS)) & 1u, abort_flag)) { ok = false; break; }
-        fence_after();
-        if (j < nb[0]) {
-          if (!mbar_wait(p_full(0), (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
-          fence_after();
-          issue_pv(0, vs, j);
+      // Event-driven issue: each tile has an S stream and a P V stream; whichever has its inputs
+      // ready goes next, so S of the next key block is usually in flight while softmax runs.
+      int sj[2] = {0, 0}, pj[2] = {0, 0};
+      int k_rel = 0, v_rel = 0;
+      uint32_t idle = 0;
+      while (ok && (pj[0] < nb[0] || pj[1] < nb[1])) {
+        bool progress = false;
+#pragma unroll
+        for (int t = 0; t < 2; t++) {
+          if (sj[t] < nb[t]) {
+            const int j = sj[t];
+            if (mbar_try_wait(k_full(j % C::KS), ((uint32_t)(j / C::KS)) & 1u) &&
+                (j == 0 || mbar_try_wait(s_free(t), (uint32_t)(j - 1) & 1u))) {
+              fence_after();
+              issue_s(t, j % C::KS);
+              sj[t]++;
+              progress = true;
+            }
+          }
+          while (k_rel < nb_max && (sj[0] > k_rel || k_rel >= nb[0]) && (sj[1] > k_rel || k_rel >= nb[1])) {
+            umma_commit(k_empty(k_rel % C::KS));
+            k_rel++;
+          }
+          if (pj[t] < nb[t]) {
+            const int j = pj[t];
+            if (mbar_try_wait(v_full(j % C::VS), ((uint32_t)(j / C::VS)) & 1u) && mbar_try_wait(p_full(t), (uint32_t)j & 1u)) {
+              fence_after();
+              issue_pv(t, j % C::VS, j);
+              pj[t]++;
+              progress = true;
+            }
+          }
+          while (v_rel < nb_max && (pj[0] > v_rel || v_rel >= nb[0]) && (pj[1] > v_rel || v_rel >= nb[1])) {
+            umma_commit(v_empty(v_rel % C::VS));
+            v_rel++;
+          }
         }
-        if (j + 1 < nb_max) {
-          if (!mbar_wait(k_full(ks1), ((uint32_t)((j + 1) / C::KS)) & 1u, abort_flag)) { ok = false; break; }
-          fence_after();
-          if (j + 1 < nb[0]) issue_s(0, ks1);
-        }
-        if (j < nb[1]) {
-          if (!mbar_wait(p_full(1), (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
-          fence_after();
-          issue_pv(1, vs, j);
-        }
-        umma_commit(v_empty(vs));
-        if (j + 1 < nb_max) {
-          if (j + 1 < nb[1]) issue_s(1, ks1);
-          umma_commit(k_empty(ks1));
+        if (progress) {
+          idle = 0;
+        } else if (++idle > WAIT_LIMIT || ((idle & 255u) == 0 && *abort_flag)) {
+          *abort_flag = 1;
+          ok = false;
         }
       }
       if (!ok) atomicExch(&g_fa_status[0], 2u);
@@ -210,66 +228,66 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     for (int j = 0; j < n_my; j++) {
       if (!mbar_wait(s_full(t), (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
       fence_after();
+      uint32_t r[128];
+      tmem_ld32(ts_addr, r);
+      tmem_ld32(ts_addr + 32, r + 32);
+      tmem_ld32(ts_addr + 64, r + 64);
+      tmem_ld32(ts_addr + 96, r + 96);
+      tmem_ld_wait();
+      fence_before();
+      mbar_arrive(s_free(t));                       // S_t may be overwritten by the next key block
       const int c0 = j * C::BN;
       const int warp_row0 = m0 + t * C::BM + quad * 32;
       const bool need_mask = (c0 + C::BN > p.Sk) || (p.causal && (c0 + C::BN - 1 > warp_row0 + off));
-      const int lim = p.causal ? min(p.Sk - 1, row + off) : p.Sk - 1;   // last visible key of this row
-      // pass 1: row maximum
+      const int lim = (p.causal ? min(p.Sk - 1, row + off) : p.Sk - 1) - c0;   // last visible column of this block
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < C::BN / 32; c++) {
-        uint32_t r[32];
-        tmem_ld32(ts_addr + c * 32, r);
-        tmem_ld_wait();
-        if (need_mask) {
+      if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; i++) if (c0 + c * 32 + i <= lim) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int i = 0; i < 128; i++) {
+          if (i > lim) r[i] = 0xff800000u;           // -inf
+          mx = fmaxf(mx, __uint_as_float(r[i]));
         }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 128; i++) mx = fmaxf(mx, __uint_as_float(r[i]));
       }
-      const float m_new = fmaxf(m_i, mx);
+      // Lazy reference maximum: keep the old one unless the new maximum is more than 2^8 above
+      // it, so that O and l rarely need rescaling (values stay below 2^8 relative to it).
+      float m_new = fmaxf(m_i, mx);
+      if (m_i != -INFINITY && (m_new - m_i) * sl2 <= 8.f) m_new = m_i;
       const float m_s = (m_new == -INFINITY) ? 0.f : m_new * sl2;
       const float corr = (m_i == -INFINITY) ? 0.f : exp2f(m_i * sl2 - m_s);
+      float rs = 0.f;
+      uint32_t pb[64];
+#pragma unroll
+      for (int i = 0; i < 128; i += 2) {
+        const float e0 = exp2f(fmaf(__uint_as_float(r[i]), sl2, -m_s));
+        const float e1 = exp2f(fmaf(__uint_as_float(r[i + 1]), sl2, -m_s));
+        rs += e0 + e1;
+        bf162 pk = __floats2bfloat162_rn(e0, e1);
+        pb[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+      }
       if (j > 0) {
         // previous P V finished: O is stable and the P buffer may be overwritten
         if (!mbar_wait(pv_done(t), (uint32_t)(j - 1) & 1u, abort_flag)) { ok = false; break; }
         fence_after();
-        if (__any_sync(0xffffffffu, m_new > m_i)) {
+        if (__any_sync(0xffffffffu, m_new != m_i)) {
 #pragma unroll 1
           for (int c = 0; c < D / 32; c++) {
-            uint32_t r[32];
-            tmem_ld32(to_addr + c * 32, r);
+            uint32_t o[32];
+            tmem_ld32(to_addr + c * 32, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
-            tmem_st32(to_addr + c * 32, r);
+            for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+            tmem_st32(to_addr + c * 32, o);
           }
           tmem_st_wait();
         }
       }
-      // pass 2: P = exp2(s*scale - max), row sum, bf16 P into swizzled smem
-      float rs = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < C::BN / 32; c++) {
-        uint32_t r[32];
-        tmem_ld32(ts_addr + c * 32, r);
-        tmem_ld_wait();
-        float f[32];
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
-          float e = exp2f(__uint_as_float(r[i]) * sl2 - m_s);
-          if (need_mask && (c0 + c * 32 + i > lim)) e = 0.f;
-          f[i] = e;
-          rs += e;
-        }
-#pragma unroll
-        for (int g = 0; g < 4; g++) {
-          const int cc = c * 4 + g;                    // 16-byte chunk index inside the 128-key row
-          *reinterpret_cast<uint4*>(sP + (cc >> 3) * C::ATOM_BYTES + sw128_off(rit, cc & 7)) = pack8(f + g * 8);
-        }
-      }
+      for (int cc = 0; cc < 16; cc++)
+        *reinterpret_cast<uint4*>(sP + (cc >> 3) * C::ATOM_BYTES + sw128_off(rit, cc & 7)) =
+            make_uint4(pb[cc * 4], pb[cc * 4 + 1], pb[cc * 4 + 2], pb[cc * 4 + 3]);
       l_i = l_i * corr + rs;
       m_i = m_new;
       fence_before();

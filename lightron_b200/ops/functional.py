@@ -313,8 +313,10 @@ def flash_bwd_native(q, k, v, o, lse, do, causal: bool, scale: float, dq=None, d
     for t in (dq, dk, dv):
         _check_attn_layout(t)
     delta = torch.empty(B, hq, Sq, dtype=torch.float32, device=q.device)
-    dq_acc = torch.zeros(B, Sq, hq, d, dtype=torch.float32, device=q.device)
     use_tc = d in (64, 128) and not (causal and Sk < Sq) and os.environ.get("LIGHTRON_FA_BWD", "tc") == "tc"
+    # fp32 dQ accumulator: the tcgen05 kernel uses a tile-permuted layout padded to 128-row tiles
+    n_acc = B * hq * ((Sq + 127) // 128) * 128 * d if use_tc else B * Sq * hq * d
+    dq_acc = torch.zeros(n_acc, dtype=torch.float32, device=q.device)
     native.call("lb_flash_bwd_tc" if use_tc else "lb_flash_bwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
                 delta.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                 B, Sq, Sk, hq, hkv, d, q.stride(1), k.stride(1), v.stride(1), o.stride(1), do.stride(1),
