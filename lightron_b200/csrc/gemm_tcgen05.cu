@@ -17,6 +17,7 @@
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer,
 // warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w%4) .. +31).
 #include <cuda.h>
+#include <string.h>
 #include "common.cuh"
 
 // Device-side status words of the GEMM kernels.  A bounded wait that runs out sets word 0 to a
@@ -132,6 +133,35 @@ struct GemmParams {
   int tiles_m, tiles_n, num_tiles, num_kb;
 };
 
+// Extra arguments of the fused compute + collective variants (tensor-parallel group of n ranks
+// whose buffers are mapped into every rank's address space; all pointers below are usable from
+// this GPU, peers' ones go over NVLink).
+//   MODE 1, all-gather -> GEMM:  A = gather_over_ranks(x_local)  [M, K], this rank owns rows
+//     [rank * rows_per_rank, ...).  CTAs 0 .. n_comm-1 pull the peers' row blocks (plain 16-byte
+//     loads through peer pointers) into `gathered` (a normal local tensor, also the copy that
+//     backward keeps), publishing one flag per 128-row block; the other CTAs run the tcgen05 main
+//     loop over tiles ordered so that local rows come first, and gate each tile on its flag.
+//   MODE 2, GEMM -> reduce-scatter:  every rank computes partial C = A_local B_local^T [M, N];
+//     the epilogue stores each tile straight into the owner's receive area (peer stores),
+//     counts it in the owner's flag word, and after its last tile every CTA reduces the row
+//     blocks this rank owns as soon as all partials of a block have arrived.
+constexpr int MAX_RANKS = 8;
+struct CommParams {
+  int n_ranks, rank, rows_per_rank, blocks_per_rank;   // blocks of BM rows
+  int n_comm;                                          // MODE 1: CTAs that move data
+  unsigned int epoch;                                  // MODE 1: flag value of this call
+  unsigned int rs_target;                              // MODE 2: counter value when a block is complete
+  const bf16* src[MAX_RANKS];                          // MODE 1: every rank's x_local [rows_per_rank, K] (row stride ld_src)
+  long long ld_src;
+  bf16* gathered;                                      // MODE 1: local [M, K] contiguous
+  unsigned int* ready_peer[MAX_RANKS];                 // MODE 1: rank r's ready flags [n_ranks]; I write ready_peer[r][rank]
+  unsigned int* block_flags;                           // MODE 1: local [tiles_m]
+  bf16* recv[MAX_RANKS];                               // MODE 2: rank r's receive area [n_ranks][rows_per_rank][N]
+  unsigned int* rs_flags[MAX_RANKS];                   // MODE 2: rank r's counters [n_ranks][blocks_per_rank]
+  bf16* out;                                           // MODE 2: reduced [rows_per_rank, N]
+  long long ld_out;
+};
+
 __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& tm, int& tn) {
   const int group_size = GROUP_M * p.tiles_n;
   const int group = t / group_size;
@@ -142,9 +172,44 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& tm,
   tn = in_group / gsz;
 }
 
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_sys_add(unsigned int* p, unsigned int v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait on a flag written by another CTA or another GPU: gives up after ~20 s of wall
+// time (ranks may be skewed by seconds at start-up), records the failure and returns false.
+constexpr unsigned long long FLAG_WAIT_NS = 20ull * 1000ull * 1000ull * 1000ull;
+__device__ __forceinline__ bool flag_wait_ge(const unsigned int* f, unsigned int target, unsigned where) {
+  if ((int)(ld_acquire_sys(f) - target) >= 0) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  while (true) {
+    for (int i = 0; i < 64; i++) {
+      if ((int)(ld_acquire_sys(f) - target) >= 0) return true;
+      __nanosleep(64);
+    }
+    if (globaltimer_ns() - t0 > FLAG_WAIT_NS) break;
+  }
+  atomicExch(&g_lb_dev_status[0], 2u);
+  atomicExch(&g_lb_dev_status[1], where);
+  return false;
+}
+
+template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 bf16* __restrict__ C, const GemmParams p) {
+                 bf16* __restrict__ C, const GemmParams p, const CommParams cp) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -154,12 +219,68 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+
+  if (MODE == 1 && (int)blockIdx.x < cp.n_comm) {
+    // ---------------- all-gather mover CTAs (no tensor-core work, no TMEM) ----------------
+    __shared__ int s_ok;
+    if (blockIdx.x == 0 && threadIdx.x < cp.n_ranks && (int)threadIdx.x != cp.rank) {
+      // x_local was written by earlier kernels of this stream: publish it to the peers
+      __threadfence_system();
+      st_release_sys(cp.ready_peer[threadIdx.x] + cp.rank, cp.epoch);
+    }
+    const int units = cp.n_ranks * cp.blocks_per_rank;
+    const size_t row_vecs = (size_t)p.K / 8;                       // 16-byte vectors per row
+    for (int u = blockIdx.x; u < units; u += cp.n_comm) {
+      // own rows first, then the peers' (rotated so that ranks do not all hit the same peer)
+      const int src_rank = (cp.rank + u / cp.blocks_per_rank) % cp.n_ranks;
+      const int rb = u % cp.blocks_per_rank;
+      if (threadIdx.x == 0) {
+        s_ok = (src_rank == cp.rank) ? 1 : (int)flag_wait_ge(cp.ready_peer[cp.rank] + src_rank, cp.epoch, 10u);
+      }
+      __syncthreads();
+      if (s_ok) {
+        const uint4* sp = reinterpret_cast<const uint4*>(cp.src[src_rank] + (size_t)rb * BM * cp.ld_src);
+        uint4* dp = reinterpret_cast<uint4*>(cp.gathered + ((size_t)src_rank * cp.rows_per_rank + (size_t)rb * BM) * p.K);
+        const size_t src_row_vecs = (size_t)cp.ld_src / 8;
+        const size_t total = (size_t)BM * row_vecs;
+        for (size_t i = threadIdx.x; i < total; i += 4 * NUM_THREADS) {   // 4 independent loads in flight
+          uint4 v[4];
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const size_t e = i + (size_t)j * NUM_THREADS;
+            if (e < total) v[j] = __ldcv(sp + (e / row_vecs) * src_row_vecs + (e % row_vecs));   // never a stale L1 line
+          }
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const size_t e = i + (size_t)j * NUM_THREADS;
+            if (e < total) dp[e] = v[j];
+          }
+        }
+      }
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) st_release_sys(cp.block_flags + src_rank * cp.blocks_per_rank + rb, cp.epoch);
+    }
+    return;
+  }
+
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_base = smem_u32(bars);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  // persistent tile walk of this CTA
+  const int cta = (MODE == 1) ? (int)blockIdx.x - cp.n_comm : (int)blockIdx.x;
+  const int n_cta = (MODE == 1) ? (int)gridDim.x - cp.n_comm : (int)gridDim.x;
+  // m-block rotation: MODE 1 starts with the rows this rank already has, MODE 2 ends with the
+  // rows this rank keeps (so that tiles that must travel are produced first)
+  const int m_rot = (MODE == 1) ? cp.rank * cp.blocks_per_rank
+                                : (MODE == 2 ? ((cp.rank + 1) % cp.n_ranks) * cp.blocks_per_rank : 0);
+  auto map_tile = [&](int t, int& tm, int& tn) {
+    tile_coords(t, p, tm, tn);
+    if (MODE != 0) { tm += m_rot; if (tm >= p.tiles_m) tm -= p.tiles_m; }
+  };
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -191,10 +312,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+      for (int t = cta; t < p.num_tiles && ok; t += n_cta) {
         int tm, tn;
-        tile_coords(t, p, tm, tn);
+        map_tile(t, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
+        if (MODE == 1) {
+          // rows of this tile must have landed in `gathered` (written by mover CTAs with plain
+          // stores): acquire the flag, then order those writes before the async-proxy reads
+          if (!flag_wait_ge(cp.block_flags + tm, cp.epoch, 11u)) { *abort_flag = 1; ok = false; break; }
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int kb = 0; kb < p.num_kb; kb++) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1u)) { ok = false; break; }
           const uint32_t fb = full_bar(stage);
@@ -230,7 +357,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
-      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x, it++) {
+      for (int t = cta; t < p.num_tiles && ok; t += n_cta, it++) {
         const int acc = it & 1;
         const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, 2u)) { ok = false; break; }
@@ -258,17 +385,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int quad = warp & 3;  // TMEM lane quadrant this warp may access
     bool ok = true;
     int it = 0;
-    for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x, it++) {
+    for (int t = cta; t < p.num_tiles && ok; t += n_cta, it++) {
       const int acc = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
       int tm, tn;
-      tile_coords(t, p, tm, tn);
+      map_tile(t, tm, tn);
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4u)) { ok = false; break; }
       tcgen05_fence_after();
       const int row = tm * BM + quad * 32 + lane;
       const int n0 = tn * BN;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * BN;
-      bf16* crow = C + (size_t)row * p.ldc + n0;
+      bf16* crow;
+      int owner = 0, lb = 0;
+      if (MODE == 2) {
+        // destination: receive area of the rank that owns this row block, slot of this rank
+        owner = tm / cp.blocks_per_rank;
+        lb = tm - owner * cp.blocks_per_rank;
+        crow = cp.recv[owner] + ((size_t)cp.rank * cp.rows_per_rank + (size_t)lb * BM + quad * 32 + lane) * p.N + n0;
+      } else {
+        crow = C + (size_t)row * p.ldc + n0;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; c++) {
         uint32_t r[32];
@@ -288,8 +424,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
       tcgen05_fence_before();
+      if (MODE == 2) __threadfence_system();   // this thread's (possibly remote) stores before the count
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (lane == 0) {
+        mbar_arrive(tempty_bar(acc));
+        if (MODE == 2) red_release_sys_add(cp.rs_flags[owner] + cp.rank * cp.blocks_per_rank + lb, 1u);
+      }
     }
   }
 
@@ -299,6 +439,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (warp == 1) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+
+  if (MODE == 2) {
+    // ---------------- reduce the row blocks this rank owns, as their partials arrive ----------------
+    __shared__ int s_ok2;
+    const int units = cp.blocks_per_rank * p.tiles_n;
+    const bf16* mine = cp.recv[cp.rank];
+    for (int u = blockIdx.x; u < units; u += gridDim.x) {
+      const int lb = u / p.tiles_n, tn = u % p.tiles_n;
+      if (threadIdx.x == 0) {
+        int good = 1;
+        for (int s = 0; s < cp.n_ranks; s++)
+          good &= (int)flag_wait_ge(cp.rs_flags[cp.rank] + s * cp.blocks_per_rank + lb, cp.rs_target, 20u);
+        s_ok2 = good;
+      }
+      __syncthreads();
+      const int n0 = tn * BN;
+      const int ncols = min(BN, p.N - n0);
+      const int vec_per_row = ncols / 8;
+      for (int i = threadIdx.x; i < BM * vec_per_row; i += NUM_THREADS) {
+        const int r = i / vec_per_row, v = i % vec_per_row;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < cp.n_ranks; s++) {
+          float f[8];
+          unpack8(__ldcg(reinterpret_cast<const uint4*>(mine + ((size_t)s * cp.rows_per_rank + (size_t)lb * BM + r) * p.N + n0 + v * 8)), f);
+#pragma unroll
+          for (int k = 0; k < 8; k++) acc[k] += f[k];
+        }
+        *reinterpret_cast<uint4*>(cp.out + ((size_t)lb * BM + r) * cp.ld_out + n0 + v * 8) = pack8(acc);
+      }
+      __syncthreads();
+    }
   }
 }
 
@@ -381,7 +553,9 @@ extern "C" int lb_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   }
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.a_mn = a_mn; p.b_mn = b_mn;
@@ -390,7 +564,105 @@ extern "C" int lb_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   p.num_tiles = p.tiles_m * p.tiles_n;
   p.num_kb = (K + BK - 1) / BK;
   int grid = p.num_tiles < g_num_sms ? p.num_tiles : g_num_sms;
-  gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, (bf16*)C, p);
+  CommParams cp;
+  memset(&cp, 0, sizeof(cp));
+  gemm_bf16_kernel<0><<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, (bf16*)C, p, cp);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}
+
+namespace {
+int init_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaFuncSetAttribute(gemm_bf16_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  }
+  return g_num_sms;
+}
+void bind_ctx() {
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(0);
+    ctx_bound = true;
+  }
+}
+}  // namespace
+
+// All-gather -> GEMM in one kernel.  C[M,N] = gather(x)[M,K] . op(B)^T where rank r's rows
+// [r*M/n, (r+1)*M/n) are read from src_ptrs[r] (row stride ld_src; peer pointers for r != rank).
+// `gathered` [M,K] (local, contiguous) receives the gathered operand and stays valid afterwards.
+// ready_ptrs[r] = rank r's ready-flag array [n_ranks]; block_flags = local array [M/128]; both
+// zero-initialised once; `epoch` must grow by one per call that uses these flags.
+// M must be a multiple of 128 * n_ranks.  src_ptrs / ready_ptrs are host arrays of n_ranks pointers.
+extern "C" int lb_gemm_ag(const void* B, void* C, int M, int N, int K, long long ldb, long long ldc, int b_mn,
+                          int n_ranks, int rank, const void* const* src_ptrs, long long ld_src, void* gathered,
+                          void* const* ready_ptrs, void* block_flags, unsigned int epoch, int n_comm, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || n_ranks < 2 || n_ranks > MAX_RANKS) return LB_ERR_SHAPE;
+  if ((ldb % 8) || (ldc % 8) || (N % 8) || (K % 8) || (ld_src % 8) || (M % (BM * n_ranks))) return LB_ERR_SHAPE;
+  bind_ctx();
+  CUtensorMap ta, tb;
+  int rc = make_map(&ta, gathered, (uint64_t)K, (uint64_t)M, (uint64_t)K, BK, BM);
+  if (rc) return rc;
+  if (!b_mn) rc = make_map(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, BN);
+  else       rc = make_map(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK);
+  if (rc) return rc;
+  const int sms = init_sms();
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.a_mn = 0; p.b_mn = b_mn;
+  p.tiles_m = M / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.num_kb = (K + BK - 1) / BK;
+  CommParams cp;
+  memset(&cp, 0, sizeof(cp));
+  cp.n_ranks = n_ranks; cp.rank = rank; cp.rows_per_rank = M / n_ranks; cp.blocks_per_rank = cp.rows_per_rank / BM;
+  if (n_comm < 1) n_comm = 1;
+  if (n_comm > sms / 2) n_comm = sms / 2;
+  cp.n_comm = n_comm; cp.epoch = epoch;
+  for (int r = 0; r < n_ranks; r++) { cp.src[r] = (const bf16*)src_ptrs[r]; cp.ready_peer[r] = (unsigned int*)ready_ptrs[r]; }
+  cp.ld_src = ld_src; cp.gathered = (bf16*)gathered; cp.block_flags = (unsigned int*)block_flags;
+  int n_gemm = sms - n_comm;
+  if (n_gemm > p.num_tiles) n_gemm = p.num_tiles;
+  gemm_bf16_kernel<1><<<n_comm + n_gemm, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, (bf16*)C, p, cp);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}
+
+// GEMM -> reduce-scatter in one kernel.  Every rank computes A[M,K_local] . op(B)^T; rank r ends
+// with out[M/n, N] = sum over ranks of rows [r*M/n, ...).  recv_ptrs[r] = rank r's receive area
+// [n_ranks][M/n][N] bf16, flag_ptrs[r] = rank r's counters [n_ranks][M/n/128] (zeroed once);
+// rs_target = previous target of these counters + 4 * ceil(N/256).
+extern "C" int lb_gemm_rs(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, int b_mn,
+                          int n_ranks, int rank, void* const* recv_ptrs, void* const* flag_ptrs, unsigned int rs_target,
+                          void* out, long long ld_out, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || n_ranks < 2 || n_ranks > MAX_RANKS) return LB_ERR_SHAPE;
+  if ((lda % 8) || (ldb % 8) || (ld_out % 8) || (N % 8) || (M % (BM * n_ranks))) return LB_ERR_SHAPE;
+  bind_ctx();
+  CUtensorMap ta, tb;
+  int rc = make_map(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM);
+  if (rc) return rc;
+  if (!b_mn) rc = make_map(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, BN);
+  else       rc = make_map(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK);
+  if (rc) return rc;
+  const int sms = init_sms();
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.ldc = N; p.a_mn = 0; p.b_mn = b_mn;
+  p.tiles_m = M / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.num_kb = (K + BK - 1) / BK;
+  CommParams cp;
+  memset(&cp, 0, sizeof(cp));
+  cp.n_ranks = n_ranks; cp.rank = rank; cp.rows_per_rank = M / n_ranks; cp.blocks_per_rank = cp.rows_per_rank / BM;
+  cp.rs_target = rs_target;
+  for (int r = 0; r < n_ranks; r++) { cp.recv[r] = (bf16*)recv_ptrs[r]; cp.rs_flags[r] = (unsigned int*)flag_ptrs[r]; }
+  cp.out = (bf16*)out; cp.ld_out = ld_out;
+  int grid = p.num_tiles < sms ? p.num_tiles : sms;
+  gemm_bf16_kernel<2><<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, nullptr, p, cp);
   LB_CHECK_LAUNCH();
   return LB_OK;
 }

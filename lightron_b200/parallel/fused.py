@@ -30,16 +30,16 @@ def set_fused(enabled: bool) -> None:
     _FUSED_ENABLED = bool(enabled)
 
 
-def _fused_ok(x: torch.Tensor, group) -> bool:
+def _fused_ok(x: torch.Tensor, group, total_rows: int) -> bool:
     if not (_FUSED_ENABLED and x.is_cuda and x.dtype == torch.bfloat16 and comm.group_size(group) > 1):
         return False
     from . import symm
-    return symm.supported(group)
+    return symm.supported(group) and symm.shapes_ok(total_rows, group)
 
 
 def all_gather_linear(x_local: torch.Tensor, weights: Sequence[torch.Tensor], group) -> torch.Tensor:
     """x_local [T/n, K] (this rank's rows) -> [T, sum out_i] = all_gather(x) @ cat(weights)^T."""
-    if _fused_ok(x_local, group):
+    if _fused_ok(x_local, group, x_local.shape[0] * comm.group_size(group)):
         from . import symm
         return symm.AllGatherLinear.apply(x_local, group, *weights)
     return OF.linear(comm.gather_rows(x_local, group), *weights)
@@ -47,7 +47,7 @@ def all_gather_linear(x_local: torch.Tensor, weights: Sequence[torch.Tensor], gr
 
 def linear_reduce_scatter(x: torch.Tensor, weight: torch.Tensor, group) -> torch.Tensor:
     """x [T, K/n], weight [N, K/n] -> this rank's [T/n, N] rows of sum_over_ranks(x @ w^T)."""
-    if _fused_ok(x, group):
+    if _fused_ok(x, group, x.shape[0]):
         from . import symm
         return symm.LinearReduceScatter.apply(x, weight, group)
     return comm.scatter_rows(OF.linear(x, weight), group)

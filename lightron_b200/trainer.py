@@ -89,6 +89,11 @@ class Trainer:
         if self.args.sequence_parallel and d.tp_size > 1:
             rows //= d.tp_size
         self.tensor_shapes = (rows, self.args.dim)
+        if self.args.sequence_parallel and d.tp_size > 1 and d.fused_comm and self.device.type == "cuda":
+            from .parallel import symm
+            tokens = t.micro_batch_size * self.dataloader.seq_length_per_gpu
+            if symm.supported(ctx.tp_group) and symm.shapes_ok(tokens, ctx.tp_group):
+                symm.presize(ctx.tp_group, tokens, self.args.dim, self.device)
         self.step = 0
         self.tokens_seen = 0
         self.timer = StepTimer(self.device)
