@@ -29,6 +29,7 @@ namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64;
 constexpr int STAGES = 4;
+constexpr int STAGES_DEFAULT = STAGES;
 constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -137,25 +138,27 @@ struct GemmParams {
 // whose buffers are mapped into every rank's address space; all pointers below are usable from
 // this GPU, peers' ones go over NVLink).
 //   MODE 1, all-gather -> GEMM:  A = gather_over_ranks(x_local)  [M, K], this rank owns rows
-//     [rank * rows_per_rank, ...).  CTAs 0 .. n_comm-1 pull the peers' row blocks (plain 16-byte
-//     loads through peer pointers) into `gathered` (a normal local tensor, also the copy that
-//     backward keeps), publishing one flag per 128-row block; the other CTAs run the tcgen05 main
-//     loop over tiles ordered so that local rows come first, and gate each tile on its flag.
+//     [rank * rows_per_rank, ...).  CTAs 0 .. n_comm-1 PUSH this rank's rows into every rank's
+//     gather buffer (coalesced 16-byte stores through peer pointers: stores are fire-and-forget,
+//     so a few CTAs saturate NVLink, which latency-bound remote loads cannot) and count each
+//     128-row block in the destination's flag word; the other CTAs run the tcgen05 main loop,
+//     local rows first (read straight from x_local), each remote tile gated on its flag.
 //   MODE 2, GEMM -> reduce-scatter:  every rank computes partial C = A_local B_local^T [M, N];
-//     the epilogue stores each tile straight into the owner's receive area (peer stores),
-//     counts it in the owner's flag word, and after its last tile every CTA reduces the row
-//     blocks this rank owns as soon as all partials of a block have arrived.
+//     the epilogue stages each tile in shared memory and stores it, 512 contiguous bytes per
+//     row, straight into the owner's receive area, counts it in the owner's flag word, and after
+//     its last tile every CTA reduces the row blocks this rank owns as soon as all partials of a
+//     block have arrived.
 constexpr int MAX_RANKS = 8;
+constexpr int MOVER_WARPS = NUM_THREADS / 32;
 struct CommParams {
   int n_ranks, rank, rows_per_rank, blocks_per_rank;   // blocks of BM rows
   int n_comm;                                          // MODE 1: CTAs that move data
-  unsigned int epoch;                                  // MODE 1: flag value of this call
+  unsigned int ag_target;                              // MODE 1: flag value when a block has fully arrived
   unsigned int rs_target;                              // MODE 2: counter value when a block is complete
-  const bf16* src[MAX_RANKS];                          // MODE 1: every rank's x_local [rows_per_rank, K] (row stride ld_src)
-  long long ld_src;
-  bf16* gathered;                                      // MODE 1: local [M, K] contiguous
-  unsigned int* ready_peer[MAX_RANKS];                 // MODE 1: rank r's ready flags [n_ranks]; I write ready_peer[r][rank]
-  unsigned int* block_flags;                           // MODE 1: local [tiles_m]
+  const bf16* x_local;                                 // MODE 1: this rank's rows [rows_per_rank, K], row stride ld_x
+  long long ld_x;
+  bf16* gather[MAX_RANKS];                             // MODE 1: rank r's gather buffer [M, K] contiguous
+  unsigned int* ag_flags[MAX_RANKS];                   // MODE 1: rank r's block counters [M / 128]
   bf16* recv[MAX_RANKS];                               // MODE 2: rank r's receive area [n_ranks][rows_per_rank][N]
   unsigned int* rs_flags[MAX_RANKS];                   // MODE 2: rank r's counters [n_ranks][blocks_per_rank]
   bf16* out;                                           // MODE 2: reduced [rows_per_rank, N]
@@ -206,10 +209,34 @@ __device__ __forceinline__ bool flag_wait_ge(const unsigned int* f, unsigned int
   return false;
 }
 
+// MODE 2 stages its output tile in shared memory (one padded 32 x 256 bf16 panel per epilogue warp)
+// and pays for it with one pipeline stage.
+constexpr int RS_ROW_BYTES = BN * 2 + 16;                 // padded: 16-byte stores of a warp stay conflict-free
+constexpr int RS_STAGE_BYTES = 4 * 32 * RS_ROW_BYTES;
+constexpr int STAGES_RS = 3;
+constexpr int SMEM_BYTES_RS = STAGES_RS * STAGE_BYTES + 1024 + 1024 + RS_STAGE_BYTES;
+// mover CTAs of MODE 1: ring of bulk-copy buffers
+constexpr int MV_BUF_BYTES = 32 * 1024;
+constexpr int MV_NBUF = 5;
+
+__device__ __forceinline__ void bulk_load(uint32_t sdst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(sdst),
+               "l"(gsrc), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, uint32_t ssrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(ssrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 bf16* __restrict__ C, const GemmParams p, const CommParams cp) {
+                 const __grid_constant__ CUtensorMap tmap_own, bf16* __restrict__ C, const GemmParams p,
+                 const CommParams cp) {
+  constexpr int STAGES = (MODE == 2) ? STAGES_RS : STAGES_DEFAULT;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -222,44 +249,45 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   if (MODE == 1 && (int)blockIdx.x < cp.n_comm) {
     // ---------------- all-gather mover CTAs (no tensor-core work, no TMEM) ----------------
-    __shared__ int s_ok;
-    if (blockIdx.x == 0 && threadIdx.x < cp.n_ranks && (int)threadIdx.x != cp.rank) {
-      // x_local was written by earlier kernels of this stream: publish it to the peers
-      __threadfence_system();
-      st_release_sys(cp.ready_peer[threadIdx.x] + cp.rank, cp.epoch);
-    }
+    // unit = (destination rank, 128-row block of this rank's rows).  Every warp copies its share of
+    // the block's rows (two rows = 2 x K x 2 bytes in flight per warp), fences, and adds one to the
+    // destination's counter of that block; warps never wait for each other, so while one sits in
+    // its fence the others keep streaming.  Peers first, the local copy last.
     const int units = cp.n_ranks * cp.blocks_per_rank;
-    const size_t row_vecs = (size_t)p.K / 8;                       // 16-byte vectors per row
+    const int vec_per_row = p.K / 8;
     for (int u = blockIdx.x; u < units; u += cp.n_comm) {
-      // own rows first, then the peers' (rotated so that ranks do not all hit the same peer)
-      const int src_rank = (cp.rank + u / cp.blocks_per_rank) % cp.n_ranks;
+      const int dst_rank = (cp.rank + 1 + u / cp.blocks_per_rank) % cp.n_ranks;
       const int rb = u % cp.blocks_per_rank;
-      if (threadIdx.x == 0) {
-        s_ok = (src_rank == cp.rank) ? 1 : (int)flag_wait_ge(cp.ready_peer[cp.rank] + src_rank, cp.epoch, 10u);
-      }
-      __syncthreads();
-      if (s_ok) {
-        const uint4* sp = reinterpret_cast<const uint4*>(cp.src[src_rank] + (size_t)rb * BM * cp.ld_src);
-        uint4* dp = reinterpret_cast<uint4*>(cp.gathered + ((size_t)src_rank * cp.rows_per_rank + (size_t)rb * BM) * p.K);
-        const size_t src_row_vecs = (size_t)cp.ld_src / 8;
-        const size_t total = (size_t)BM * row_vecs;
-        for (size_t i = threadIdx.x; i < total; i += 4 * NUM_THREADS) {   // 4 independent loads in flight
-          uint4 v[4];
+      const uint4* sp = reinterpret_cast<const uint4*>(cp.x_local + (size_t)rb * BM * cp.ld_x);
+      uint4* dp = reinterpret_cast<uint4*>(cp.gather[dst_rank] + ((size_t)cp.rank * cp.rows_per_rank + (size_t)rb * BM) * p.K);
+      const size_t src_row = (size_t)cp.ld_x / 8;
+      // each warp owns rows warp, warp+6, ...; it keeps 4 rows x 4 vectors (256 B per lane) in flight
+      for (int r = warp; r < BM; r += 4 * MOVER_WARPS) {
+        for (int v0 = 0; v0 < vec_per_row; v0 += 32 * 4) {
+          uint4 a[4][4];
 #pragma unroll
-          for (int j = 0; j < 4; j++) {
-            const size_t e = i + (size_t)j * NUM_THREADS;
-            if (e < total) v[j] = __ldcv(sp + (e / row_vecs) * src_row_vecs + (e % row_vecs));   // never a stale L1 line
+          for (int q = 0; q < 4; q++) {
+            const int rr = r + q * MOVER_WARPS;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const int v = v0 + j * 32 + lane;
+              if (rr < BM && v < vec_per_row) a[q][j] = sp[(size_t)rr * src_row + v];
+            }
           }
 #pragma unroll
-          for (int j = 0; j < 4; j++) {
-            const size_t e = i + (size_t)j * NUM_THREADS;
-            if (e < total) dp[e] = v[j];
+          for (int q = 0; q < 4; q++) {
+            const int rr = r + q * MOVER_WARPS;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const int v = v0 + j * 32 + lane;
+              if (rr < BM && v < vec_per_row) dp[(size_t)rr * vec_per_row + v] = a[q][j];
+            }
           }
         }
       }
-      __threadfence();
-      __syncthreads();
-      if (threadIdx.x == 0) st_release_sys(cp.block_flags + src_rank * cp.blocks_per_rank + rb, cp.epoch);
+      __threadfence_system();
+      __syncwarp();
+      if (lane == 0) red_release_sys_add(cp.ag_flags[dst_rank] + cp.rank * cp.blocks_per_rank + rb, 1u);
     }
     return;
   }
@@ -316,12 +344,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int tm, tn;
         map_tile(t, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
+        bool own = false;
         if (MODE == 1) {
-          // rows of this tile must have landed in `gathered` (written by mover CTAs with plain
-          // stores): acquire the flag, then order those writes before the async-proxy reads
-          if (!flag_wait_ge(cp.block_flags + tm, cp.epoch, 11u)) { *abort_flag = 1; ok = false; break; }
-          asm volatile("fence.proxy.async;" ::: "memory");
+          own = (tm / cp.blocks_per_rank) == cp.rank;
+          if (!own) {
+            // rows of this tile must have landed in this rank's gather buffer (pushed by a peer):
+            // acquire the flag, then order those writes before the async-proxy reads
+            if (!flag_wait_ge(cp.ag_flags[cp.rank] + tm, cp.ag_target, 11u)) { *abort_flag = 1; ok = false; break; }
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
         }
+        const int m0_own = m0 - cp.rank * cp.rows_per_rank;   // row inside this rank's own buffer
         for (int kb = 0; kb < p.num_kb; kb++) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1u)) { ok = false; break; }
           const uint32_t fb = full_bar(stage);
@@ -329,7 +362,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
           const int k0 = kb * BK;
-          if (!p.a_mn) {
+          if (MODE == 1 && own) {
+            tma_load_2d(sa, &tmap_own, k0, m0_own, fb);               // this rank's rows need no gather
+          } else if (!p.a_mn) {
             tma_load_2d(sa, &tmap_a, k0, m0, fb);                     // box {64 k, 128 m}
           } else {
 #pragma unroll
@@ -385,6 +420,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int quad = warp & 3;  // TMEM lane quadrant this warp may access
     bool ok = true;
     int it = 0;
+    constexpr int RS_MAX_PEND = 24;
+    unsigned int* rs_pend[RS_MAX_PEND];     // MODE 2: counters of tiles whose stores are not yet fenced
+    int rs_npend = 0, rs_pend_owner = -1;
     for (int t = cta; t < p.num_tiles && ok; t += n_cta, it++) {
       const int acc = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
@@ -405,6 +443,50 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       } else {
         crow = C + (size_t)row * p.ldc + n0;
       }
+      if (MODE == 2) {
+        // TMEM -> registers -> padded smem panel of this warp -> one bulk store per row (512 B) to
+        // the owner's receive area: NVLink sees large writes instead of scattered 16-byte stores.
+        uint8_t* panel = smem + STAGES * STAGE_BYTES + 1024 + (warp - 2) * (32 * RS_ROW_BYTES);
+        uint8_t* prow = panel + lane * RS_ROW_BYTES;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; c++) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[g * 8 + i]);
+            *reinterpret_cast<uint4*>(prow + c * 64 + g * 16) = pack8(f);
+          }
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));       // accumulator free: the next tile may start
+        // Counting a tile needs a system-scope fence after its stores, which costs microseconds.
+        // Tiles are ordered by destination rank, so the counts of one destination are batched:
+        // one fence when the destination changes (or the batch is full), then all its increments.
+        if (rs_npend > 0 && (owner != rs_pend_owner || rs_npend == RS_MAX_PEND)) {
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0)
+            for (int i = 0; i < rs_npend; i++) red_release_sys_add(rs_pend[i], 1u);
+          rs_npend = 0;
+        }
+        rs_pend_owner = owner;
+        rs_pend[rs_npend++] = cp.rs_flags[owner] + cp.rank * cp.blocks_per_rank + lb;
+        const int nvec = min(BN, p.N - n0) / 8;            // 16-byte vectors per row (<= 32)
+        bf16* dst0 = cp.recv[owner] + ((size_t)cp.rank * cp.rows_per_rank + (size_t)lb * BM + quad * 32) * p.N + n0;
+        if (lane < nvec) {
+#pragma unroll 8
+          for (int r = 0; r < 32; r++)                     // one 512-byte row per warp instruction
+            *reinterpret_cast<uint4*>(dst0 + (size_t)r * p.N + lane * 8) =
+                *reinterpret_cast<const uint4*>(panel + r * RS_ROW_BYTES + lane * 16);
+        }
+        __syncwarp();                                      // panel fully read before the next tile rewrites it
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; c++) {
         uint32_t r[32];
@@ -424,12 +506,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
       tcgen05_fence_before();
-      if (MODE == 2) __threadfence_system();   // this thread's (possibly remote) stores before the count
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(tempty_bar(acc));
-        if (MODE == 2) red_release_sys_add(cp.rs_flags[owner] + cp.rank * cp.blocks_per_rank + lb, 1u);
-      }
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+    if (MODE == 2 && rs_npend > 0) {
+      __threadfence_system();
+      __syncwarp();
+      if (lane == 0)
+        for (int i = 0; i < rs_npend; i++) red_release_sys_add(rs_pend[i], 1u);
     }
   }
 
@@ -442,35 +526,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
 
   if (MODE == 2) {
-    // ---------------- reduce the row blocks this rank owns, as their partials arrive ----------------
-    __shared__ int s_ok2;
-    const int units = cp.blocks_per_rank * p.tiles_n;
-    const bf16* mine = cp.recv[cp.rank];
-    for (int u = blockIdx.x; u < units; u += gridDim.x) {
-      const int lb = u / p.tiles_n, tn = u % p.tiles_n;
-      if (threadIdx.x == 0) {
-        int good = 1;
-        for (int s = 0; s < cp.n_ranks; s++)
-          good &= (int)flag_wait_ge(cp.rs_flags[cp.rank] + s * cp.blocks_per_rank + lb, cp.rs_target, 20u);
-        s_ok2 = good;
-      }
-      __syncthreads();
-      const int n0 = tn * BN;
-      const int ncols = min(BN, p.N - n0);
-      const int vec_per_row = ncols / 8;
-      for (int i = threadIdx.x; i < BM * vec_per_row; i += NUM_THREADS) {
-        const int r = i / vec_per_row, v = i % vec_per_row;
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int s = 0; s < cp.n_ranks; s++) {
-          float f[8];
-          unpack8(__ldcg(reinterpret_cast<const uint4*>(mine + ((size_t)s * cp.rows_per_rank + (size_t)lb * BM + r) * p.N + n0 + v * 8)), f);
+    // ---------------- wait until every partial of the rows this rank owns has arrived ----------------
+    // (the kernel's completion then means "receive area complete"; the n-way sum runs as a plain
+    // bandwidth-bound kernel right behind it, with the whole GPU instead of a tail of this grid)
+    const int n_flags = cp.n_ranks * cp.blocks_per_rank;
+    for (int i = blockIdx.x * NUM_THREADS + threadIdx.x; i < n_flags; i += gridDim.x * NUM_THREADS)
+      flag_wait_ge(cp.rs_flags[cp.rank] + i, cp.rs_target, 20u);
+  }
+}
+
+// out[r, c] = sum over source ranks of recv[s][r, c]; recv is this rank's receive area.
+__global__ void rs_reduce_kernel(const bf16* __restrict__ recv, bf16* __restrict__ out, int n_ranks, int rows, int N,
+                                 long long ld_out) {
+  const int vec_per_row = N / 8;
+  const long long total = (long long)rows * vec_per_row;
+  const size_t plane = (size_t)rows * N;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int v = (int)(i % vec_per_row);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < n_ranks; s++) {
+      float f[8];
+      unpack8(__ldcg(reinterpret_cast<const uint4*>(recv + s * plane + (size_t)r * N + v * 8)), f);
 #pragma unroll
-          for (int k = 0; k < 8; k++) acc[k] += f[k];
-        }
-        *reinterpret_cast<uint4*>(cp.out + ((size_t)lb * BM + r) * cp.ld_out + n0 + v * 8) = pack8(acc);
-      }
-      __syncthreads();
+      for (int k = 0; k < 8; k++) acc[k] += f[k];
     }
+    *reinterpret_cast<uint4*>(out + r * ld_out + v * 8) = pack8(acc);
   }
 }
 
@@ -555,7 +636,7 @@ extern "C" int lb_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
     cudaFuncSetAttribute(gemm_bf16_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     cudaFuncSetAttribute(gemm_bf16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    cudaFuncSetAttribute(gemm_bf16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_RS);
   }
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.a_mn = a_mn; p.b_mn = b_mn;
@@ -566,7 +647,7 @@ extern "C" int lb_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   int grid = p.num_tiles < g_num_sms ? p.num_tiles : g_num_sms;
   CommParams cp;
   memset(&cp, 0, sizeof(cp));
-  gemm_bf16_kernel<0><<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, (bf16*)C, p, cp);
+  gemm_bf16_kernel<0><<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, ta, (bf16*)C, p, cp);
   LB_CHECK_LAUNCH();
   return LB_OK;
 }
@@ -579,7 +660,7 @@ int init_sms() {
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
     cudaFuncSetAttribute(gemm_bf16_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     cudaFuncSetAttribute(gemm_bf16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    cudaFuncSetAttribute(gemm_bf16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_RS);
   }
   return g_num_sms;
 }
@@ -592,23 +673,25 @@ void bind_ctx() {
 }
 }  // namespace
 
-// All-gather -> GEMM in one kernel.  C[M,N] = gather(x)[M,K] . op(B)^T where rank r's rows
-// [r*M/n, (r+1)*M/n) are read from src_ptrs[r] (row stride ld_src; peer pointers for r != rank).
-// `gathered` [M,K] (local, contiguous) receives the gathered operand and stays valid afterwards.
-// ready_ptrs[r] = rank r's ready-flag array [n_ranks]; block_flags = local array [M/128]; both
-// zero-initialised once; `epoch` must grow by one per call that uses these flags.
-// M must be a multiple of 128 * n_ranks.  src_ptrs / ready_ptrs are host arrays of n_ranks pointers.
+// All-gather -> GEMM in one kernel.  C[M,N] = gather(x)[M,K] . op(B)^T; this rank contributes
+// x_local [M/n, K] (row stride ld_x), rows [rank*M/n, ...).  gather_ptrs[r] = rank r's gather buffer
+// [M,K] contiguous (peer pointers for r != rank); after the kernel gather_ptrs[rank] holds the whole
+// gathered operand.  flag_ptrs[r] = rank r's block counters [M/128] (zeroed once); ag_target =
+// (number of calls that used these counters, this one included) * 6.
+// M must be a multiple of 128 * n_ranks.  gather_ptrs / flag_ptrs are host arrays of n_ranks pointers.
 extern "C" int lb_gemm_ag(const void* B, void* C, int M, int N, int K, long long ldb, long long ldc, int b_mn,
-                          int n_ranks, int rank, const void* const* src_ptrs, long long ld_src, void* gathered,
-                          void* const* ready_ptrs, void* block_flags, unsigned int epoch, int n_comm, void* stream) {
+                          int n_ranks, int rank, const void* x_local, long long ld_x, void* const* gather_ptrs,
+                          void* const* flag_ptrs, unsigned int ag_target, int n_comm, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0 || n_ranks < 2 || n_ranks > MAX_RANKS) return LB_ERR_SHAPE;
-  if ((ldb % 8) || (ldc % 8) || (N % 8) || (K % 8) || (ld_src % 8) || (M % (BM * n_ranks))) return LB_ERR_SHAPE;
+  if ((ldb % 8) || (ldc % 8) || (N % 8) || (K % 8) || (ld_x % 8) || (M % (BM * n_ranks))) return LB_ERR_SHAPE;
   bind_ctx();
-  CUtensorMap ta, tb;
-  int rc = make_map(&ta, gathered, (uint64_t)K, (uint64_t)M, (uint64_t)K, BK, BM);
+  CUtensorMap ta, tb, town;
+  int rc = make_map(&ta, gather_ptrs[rank], (uint64_t)K, (uint64_t)M, (uint64_t)K, BK, BM);
   if (rc) return rc;
   if (!b_mn) rc = make_map(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, BN);
   else       rc = make_map(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK);
+  if (rc) return rc;
+  rc = make_map(&town, x_local, (uint64_t)K, (uint64_t)(M / n_ranks), (uint64_t)ld_x, BK, BM);
   if (rc) return rc;
   const int sms = init_sms();
   GemmParams p;
@@ -622,12 +705,12 @@ extern "C" int lb_gemm_ag(const void* B, void* C, int M, int N, int K, long long
   cp.n_ranks = n_ranks; cp.rank = rank; cp.rows_per_rank = M / n_ranks; cp.blocks_per_rank = cp.rows_per_rank / BM;
   if (n_comm < 1) n_comm = 1;
   if (n_comm > sms / 2) n_comm = sms / 2;
-  cp.n_comm = n_comm; cp.epoch = epoch;
-  for (int r = 0; r < n_ranks; r++) { cp.src[r] = (const bf16*)src_ptrs[r]; cp.ready_peer[r] = (unsigned int*)ready_ptrs[r]; }
-  cp.ld_src = ld_src; cp.gathered = (bf16*)gathered; cp.block_flags = (unsigned int*)block_flags;
+  cp.n_comm = n_comm; cp.ag_target = ag_target;
+  cp.x_local = (const bf16*)x_local; cp.ld_x = ld_x;
+  for (int r = 0; r < n_ranks; r++) { cp.gather[r] = (bf16*)gather_ptrs[r]; cp.ag_flags[r] = (unsigned int*)flag_ptrs[r]; }
   int n_gemm = sms - n_comm;
   if (n_gemm > p.num_tiles) n_gemm = p.num_tiles;
-  gemm_bf16_kernel<1><<<n_comm + n_gemm, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, (bf16*)C, p, cp);
+  gemm_bf16_kernel<1><<<n_comm + n_gemm, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, town, (bf16*)C, p, cp);
   LB_CHECK_LAUNCH();
   return LB_OK;
 }
@@ -662,7 +745,11 @@ extern "C" int lb_gemm_rs(const void* A, const void* B, int M, int N, int K, lon
   for (int r = 0; r < n_ranks; r++) { cp.recv[r] = (bf16*)recv_ptrs[r]; cp.rs_flags[r] = (unsigned int*)flag_ptrs[r]; }
   cp.out = (bf16*)out; cp.ld_out = ld_out;
   int grid = p.num_tiles < sms ? p.num_tiles : sms;
-  gemm_bf16_kernel<2><<<grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, nullptr, p, cp);
+  gemm_bf16_kernel<2><<<grid, NUM_THREADS, SMEM_BYTES_RS, (cudaStream_t)stream>>>(ta, tb, ta, nullptr, p, cp);
+  LB_CHECK_LAUNCH();
+  const long long total = (long long)cp.rows_per_rank * (N / 8);
+  int rblocks = (int)((total + 255) / 256 > sms * 8 ? sms * 8 : (total + 255) / 256);
+  rs_reduce_kernel<<<rblocks, 256, 0, (cudaStream_t)stream>>>(cp.recv[rank], cp.out, n_ranks, cp.rows_per_rank, N, ld_out);
   LB_CHECK_LAUNCH();
   return LB_OK;
 }

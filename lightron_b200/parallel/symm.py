@@ -5,15 +5,22 @@
 
 The NVLink plumbing: one symmetric allocation per tensor-parallel group
 (``torch.distributed._symmetric_memory``: every rank maps every peer's buffer), holding
- * ready flags and reduce-scatter counters (32-bit words, zeroed once, then only ever growing:
-   every call knows the value that means "this call's data", so nothing is reset), and
- * two slots each for all-gather sources and reduce-scatter receive areas.  Two slots are enough
-   without acknowledgements: a rank can only start call c+1 after every peer has entered call c+1
-   (it needs their data), i.e. after they finished reading / reducing call c.
+ * block counters (32-bit words, zeroed once, then only ever growing: every call knows the value
+   that means "this call's data has arrived", so nothing is ever reset),
+ * a ring of gather buffers ``[tokens, width]`` that peers PUSH their rows into.  Forward gathers
+   are kept for backward (wgrad needs the gathered operand), so the ring holds two micro-batch
+   generations of forward calls: a buffer is rewritten only after every rank has gone through a
+   whole further forward + backward, i.e. long after its last reader.  With 180 GB per GPU this
+   costs a few GB and removes both the re-gather and any copy out of peer-visible memory;
+ * a 2-deep ring of gather buffers for backward-only gathers and a 2-deep ring of
+   reduce-scatter receive areas.  Two are enough without acknowledgements: a rank can only
+   start call c+2 after every peer has entered call c+1 (it needs their data), i.e. after they
+   finished reading call c.
 
-The kernels read peers with plain loads and write peers with plain stores from the GEMM
-epilogue; no TMA multicast, no library kernel is ever handed a peer pointer.  Every wait on a
-peer's flag is bounded in the kernel and reports through ``lb_device_status``.
+The kernels write peers with plain coalesced stores (stores are fire-and-forget, so a few CTAs
+fill NVLink) and read only local memory; no TMA multicast, no library kernel is ever handed a
+peer pointer.  Every wait on a peer's counter is bounded in the kernel and reports through
+``lb_device_status``.
 
 Reference counterparts: ``funcol.all_gather_tensor`` + ``F.linear`` and ``F.linear`` +
 ``funcol.reduce_scatter_tensor`` (parallel/parallel_tp.py:61-69, 100-106).
@@ -22,7 +29,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Dict, List, Optional
+from typing import Dict, List
 
 import torch
 import torch.distributed as dist
@@ -31,38 +38,54 @@ from ..ops import functional as OF
 from ..ops import native
 
 _BM = 128
-_FLAG_BYTES = 128 * 1024
-_READY_OFF = 0                 # [2 slots][8 ranks] u32
-_RS_OFF = 256                  # [2 slots][n][blocks_per_rank] u32
+_MAX_BLOCKS = 4096             # 128-row blocks per gather buffer (tokens <= 524288)
 _MAX_BPR = 1024
-N_COMM_CTAS = int(os.environ.get("LIGHTRON_AG_CTAS", "16"))
+_MOVER_WARPS = 6               # warps per mover CTA: each adds 1 to a block counter
+N_COMM_CTAS = int(os.environ.get("LIGHTRON_AG_CTAS", "0"))     # 0 = choose per call from the GEMM size
+DEFAULT_KEEP_SLOTS = 8
+
+
+def _up(x: int, a: int = 256) -> int:
+    return (x + a - 1) // a * a
 
 
 class Workspace:
-    def __init__(self, group, src_bytes: int, recv_bytes: int, device):
+    """Symmetric buffer layout (bytes):
+    [ag counters: (keep + 2) x MAX_BLOCKS u32][rs counters: 2 x 8 x MAX_BPR u32]
+    [keep gather ring][2 scratch gather buffers][2 receive areas]"""
+
+    def __init__(self, group, gather_bytes: int, recv_bytes: int, keep_slots: int, device):
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group
         self.n = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
-        self.src_bytes = (src_bytes + 255) // 256 * 256
-        self.recv_bytes = (recv_bytes + 255) // 256 * 256
-        total = _FLAG_BYTES + 2 * self.src_bytes + 2 * self.recv_bytes
+        self.gather_bytes = _up(gather_bytes)
+        self.recv_bytes = _up(recv_bytes)
+        self.keep_slots = keep_slots
+        self.n_gather = keep_slots + 2
+        self.ag_flag_off = 0
+        self.rs_flag_off = _up(self.n_gather * _MAX_BLOCKS * 4)
+        self.data_off = _up(self.rs_flag_off + 2 * 8 * _MAX_BPR * 4, 4096)
+        self.recv_off0 = self.data_off + self.n_gather * self.gather_bytes
+        total = self.recv_off0 + 2 * self.recv_bytes
         self.buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
-        self.buf.zero_()
+        self.buf[: self.data_off].zero_()
         self.hdl = symm_mem.rendezvous(self.buf, group=group)
         self.ptrs: List[int] = [int(p) for p in self.hdl.buffer_ptrs]
         torch.cuda.synchronize()
-        dist.barrier(group=group)            # everybody's flags are zero before anybody signals
-        self.block_flags = torch.zeros(2, 4 * _MAX_BPR, dtype=torch.int32, device=device)   # local only
-        self.ag_calls = 0
+        dist.barrier(group=group)            # everybody's counters are zero before anybody pushes
+        self.keep_calls = 0
+        self.scratch_calls = 0
         self.rs_calls = 0
+        self.ag_uses = [0] * self.n_gather   # how often each gather buffer has been a destination
+        self.generation = [0] * self.n_gather
         self.rs_target = [0, 0]
 
-    def src_off(self, slot: int) -> int:
-        return _FLAG_BYTES + slot * self.src_bytes
+    def gather_off(self, slot: int) -> int:
+        return self.data_off + slot * self.gather_bytes
 
     def recv_off(self, slot: int) -> int:
-        return _FLAG_BYTES + 2 * self.src_bytes + slot * self.recv_bytes
+        return self.recv_off0 + slot * self.recv_bytes
 
     def local_view(self, off: int, rows: int, cols: int) -> torch.Tensor:
         return self.buf[off:off + rows * cols * 2].view(torch.bfloat16).view(rows, cols)
@@ -72,6 +95,17 @@ class Workspace:
         for r in range(self.n):
             arr[r] = self.ptrs[r] + off
         return arr
+
+    def next_gather_slot(self, keep: bool) -> int:
+        if keep:
+            slot = self.keep_calls % self.keep_slots
+            self.keep_calls += 1
+        else:
+            slot = self.keep_slots + self.scratch_calls % 2
+            self.scratch_calls += 1
+        self.ag_uses[slot] += 1
+        self.generation[slot] += 1
+        return slot
 
 
 _WS: Dict[int, Workspace] = {}
@@ -95,24 +129,26 @@ def supported(group) -> bool:
 
 def shapes_ok(rows_total: int, group) -> bool:
     n = dist.get_world_size(group)
-    return rows_total % (_BM * n) == 0 and rows_total // n // _BM <= _MAX_BPR
+    return rows_total % (_BM * n) == 0 and rows_total // _BM <= _MAX_BLOCKS and rows_total // n // _BM <= _MAX_BPR
 
 
-def workspace(group, src_bytes: int, recv_bytes: int, device) -> Workspace:
+def workspace(group, gather_bytes: int, recv_bytes: int, device, keep_slots: int = 0) -> Workspace:
+    """The group's workspace, (re)created collectively when a larger one is needed."""
     ws = _WS.get(id(group))
-    if ws is None or ws.src_bytes < src_bytes or ws.recv_bytes < recv_bytes:
+    if ws is None or ws.gather_bytes < gather_bytes or ws.recv_bytes < recv_bytes or ws.keep_slots < keep_slots:
         if ws is not None:
             torch.cuda.synchronize()
             dist.barrier(group=group)
-            src_bytes, recv_bytes = max(src_bytes, ws.src_bytes), max(recv_bytes, ws.recv_bytes)
-        ws = _WS[id(group)] = Workspace(group, src_bytes, recv_bytes, device)
+            gather_bytes, recv_bytes = max(gather_bytes, ws.gather_bytes), max(recv_bytes, ws.recv_bytes)
+            keep_slots = max(keep_slots, ws.keep_slots)
+        ws = _WS[id(group)] = Workspace(group, gather_bytes, recv_bytes, max(keep_slots, DEFAULT_KEEP_SLOTS), device)
     return ws
 
 
-def presize(group, tokens: int, width: int, device) -> None:
-    """Create the workspace once with room for [tokens, width] activations (avoids regrowth)."""
-    n = dist.get_world_size(group)
-    workspace(group, (tokens // n) * width * 2, tokens * width * 2, device)
+def presize(group, tokens: int, width: int, device, fwd_gathers_in_flight: int = 4) -> None:
+    """Create the workspace once: [tokens, width] activations, and a keep ring of twice the number
+    of forward gathers that can be alive between a forward and its backward."""
+    workspace(group, tokens * width * 2, tokens * width * 2, device, keep_slots=2 * fwd_gathers_in_flight)
 
 
 def check_status() -> None:
@@ -126,27 +162,31 @@ def check_status() -> None:
 # ---- raw ops ------------------------------------------------------------------------------------------
 
 
-def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False):
+def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, keep: bool = False):
     """x_local [M/n, K] (this rank's rows), w [N, K] (or [K, N] with b_mn) ->
-    (y [M, N] = gather(x) op(w)^T, gathered [M, K])."""
+    (y [M, N] = gather(x) op(w)^T, gathered [M, K], (slot, generation)).
+    ``gathered`` is a view of the workspace: with ``keep`` it stays valid for two micro-batch
+    generations of forward gathers, otherwise until the call after the next."""
     n = dist.get_world_size(group)
     rows, K = x_local.shape
     M = rows * n
     N = w.shape[1] if b_mn else w.shape[0]
-    ws = workspace(group, rows * K * 2, 0, x_local.device)
-    slot = ws.ag_calls % 2
-    epoch = ws.ag_calls // 2 + 1
-    ws.ag_calls += 1
-    src = ws.local_view(ws.src_off(slot), rows, K)
-    src.copy_(x_local)                               # stage this rank's rows where peers can read them
-    gathered = torch.empty(M, K, dtype=x_local.dtype, device=x_local.device)
+    ws = workspace(group, M * K * 2, 0, x_local.device)
+    slot = ws.next_gather_slot(keep)
+    target = ws.ag_uses[slot] * _MOVER_WARPS
     y = torch.empty(M, N, dtype=x_local.dtype, device=x_local.device)
-    ready = ws.ptr_array(_READY_OFF + slot * 8 * 4)
-    srcs = ws.ptr_array(ws.src_off(slot))
+    # CTAs that push rows instead of doing MMAs: a short GEMM needs the gather done quickly (more
+    # movers), a long one hides it behind the math anyway (fewer movers, more tensor-core SMs).
+    n_comm = N_COMM_CTAS
+    if n_comm <= 0:
+        flops = 2.0 * M * N * K
+        n_comm = 32 if flops < 1.2e11 else (16 if flops < 6e11 else 8)
+    gathers = ws.ptr_array(ws.gather_off(slot))
+    flags = ws.ptr_array(ws.ag_flag_off + slot * _MAX_BLOCKS * 4)
     native.call("lb_gemm_ag", w.data_ptr(), y.data_ptr(), M, N, K, w.stride(0), y.stride(0), int(b_mn), n, ws.rank,
-                srcs, K, gathered.data_ptr(), ready, ws.block_flags[slot].data_ptr(), epoch, N_COMM_CTAS,
-                native.stream_ptr())
-    return y, gathered
+                x_local.data_ptr(), x_local.stride(0), gathers, flags, target, n_comm, native.stream_ptr())
+    gathered = ws.local_view(ws.gather_off(slot), M, K)
+    return y, gathered, (slot, ws.generation[slot])
 
 
 def gemm_rs(x: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False) -> torch.Tensor:
@@ -159,11 +199,11 @@ def gemm_rs(x: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False) -> torc
     slot = ws.rs_calls % 2
     ws.rs_calls += 1
     bpr = M // n // _BM
+    assert bpr <= _MAX_BPR
     ws.rs_target[slot] += 4 * ((N + 255) // 256)
     out = torch.empty(M // n, N, dtype=x.dtype, device=x.device)
     recv = ws.ptr_array(ws.recv_off(slot))
-    flags = ws.ptr_array(_RS_OFF + slot * 8 * _MAX_BPR * 4)
-    assert bpr <= _MAX_BPR
+    flags = ws.ptr_array(ws.rs_flag_off + slot * 8 * _MAX_BPR * 4)
     native.call("lb_gemm_rs", x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0), w.stride(0), int(b_mn), n, ws.rank,
                 recv, flags, ws.rs_target[slot], out.data_ptr(), out.stride(0), native.stream_ptr())
     return out
@@ -176,19 +216,25 @@ class AllGatherLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_local, group, *ws):
         fused = OF._rows_adjacent(ws)
-        wcat = OF._as_strided_cat(ws) if fused else None
+        x_local = x_local.contiguous()
         if fused:
-            y, gathered = ag_gemm(x_local.contiguous(), wcat, group)
+            y, gathered, tag = ag_gemm(x_local, OF._as_strided_cat(ws), group, keep=True)
         else:
-            y0, gathered = ag_gemm(x_local.contiguous(), ws[0], group)
+            y0, gathered, tag = ag_gemm(x_local, ws[0], group, keep=True)
             y = torch.cat([y0] + [OF.gemm(gathered, w) for w in ws[1:]], dim=1)
-        ctx.save_for_backward(gathered, *ws)
+        ctx.save_for_backward(*ws)
+        ctx.gathered, ctx.tag = gathered, tag
         ctx.group, ctx.fused = group, fused
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        gathered, *ws = ctx.saved_tensors
+        ws = ctx.saved_tensors
+        gathered, (slot, gen) = ctx.gathered, ctx.tag
+        wsp = _WS[id(ctx.group)]
+        if wsp.generation[slot] != gen:
+            raise RuntimeError("gathered activation was overwritten before its backward: the keep ring of the "
+                               "peer-memory workspace is too small (symm.presize(..., fwd_gathers_in_flight=...))")
         dy = dy.contiguous()
         sizes = [w.shape[0] for w in ws]
         if ctx.fused:
@@ -220,6 +266,6 @@ class LinearReduceScatter(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy_local):
         x, w = ctx.saved_tensors
-        dx, dy_full = ag_gemm(dy_local.contiguous(), w, ctx.group, b_mn=True)
+        dx, dy_full, _ = ag_gemm(dy_local.contiguous(), w, ctx.group, b_mn=True, keep=False)
         dw = OF.gemm(dy_full, x, a_mn=True, b_mn=True)
         return dx, dw, None

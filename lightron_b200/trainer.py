@@ -93,7 +93,10 @@ class Trainer:
             from .parallel import symm
             tokens = t.micro_batch_size * self.dataloader.seq_length_per_gpu
             if symm.supported(ctx.tp_group) and symm.shapes_ok(tokens, ctx.tp_group):
-                symm.presize(ctx.tp_group, tokens, self.args.dim, self.device)
+                n_layers = len(net.layers)
+                per_mb = 2 * n_layers + (1 if net.last_stage else 0)
+                in_flight = 1 if d.pp_size == 1 else (d.pp_size if d.pp_engine == "1f1b" else t.gradient_accumulation_steps)
+                symm.presize(ctx.tp_group, tokens, self.args.dim, self.device, fwd_gathers_in_flight=per_mb * in_flight)
         self.step = 0
         self.tokens_seen = 0
         self.timer = StepTimer(self.device)

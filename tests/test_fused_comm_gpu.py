@@ -26,7 +26,7 @@ for it, (M, N, K) in enumerate([(256 * world, 512, 256), (1024 * world, 1280, 51
     w = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16)
     rows = M // world
     x_local = xf[rank * rows:(rank + 1) * rows].contiguous()
-    y, gathered = symm.ag_gemm(x_local, w, g)
+    y, gathered, _ = symm.ag_gemm(x_local, w, g)
     torch.cuda.synchronize()
     assert torch.equal(gathered, xf), f"gathered mismatch it={it}"
     want = xf.float() @ w.float().t()
@@ -41,7 +41,7 @@ for it, (M, N, K) in enumerate([(256 * world, 512, 256), (1024 * world, 1280, 51
     assert rel(out, want_rs) < 1e-2, f"gemm_rs rel {rel(out, want_rs)} it={it}"
     # b_mn variants (backward shapes)
     wt = w.t().contiguous()                  # [K, N] storage
-    y2, _ = symm.ag_gemm(x_local, wt, g, b_mn=True)
+    y2, _, _ = symm.ag_gemm(x_local, wt, g, b_mn=True)
     assert rel(y2, want) < 5e-3
 symm.check_status()
 # autograd parity with the library-collective path
