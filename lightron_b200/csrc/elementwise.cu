@@ -351,7 +351,7 @@ __global__ void __launch_bounds__(256) ce_stats_kernel(const bf16* __restrict__ 
   __shared__ float sm[8], ss[8];
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   float wm = warp_max(m);
-  s = warp_sum(s * __expf(m - wm));
+  s = warp_sum(m == -INFINITY ? 0.f : s * __expf(m - wm));   // lanes without elements (V < 8 * threads)
   if (lane == 0) { sm[wid] = wm; ss[wid] = s; }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -359,7 +359,7 @@ __global__ void __launch_bounds__(256) ce_stats_kernel(const bf16* __restrict__ 
     const int nw = blockDim.x >> 5;
     for (int i = 1; i < nw; i++) gm = fmaxf(gm, sm[i]);
     float gs = 0.f;
-    for (int i = 0; i < nw; i++) gs += ss[i] * __expf(sm[i] - gm);
+    for (int i = 0; i < nw; i++) gs += (sm[i] == -INFINITY) ? 0.f : ss[i] * __expf(sm[i] - gm);
     mx_out[row] = gm;
     se_out[row] = gs;
     const long long t = tgt[row] - v0;

@@ -45,6 +45,8 @@ _SIGNATURES = {
     "lb_gemm_bf16": [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _I, _P],
     "lb_gemm_ag": [_P, _P, _I, _I, _I, _L, _L, _I, _I, _I, _P, _L, _P, _P, ctypes.c_uint, _I, _P],
     "lb_gemm_rs": [_P, _P, _I, _I, _I, _L, _L, _I, _I, _I, _P, _P, ctypes.c_uint, _P, _L, _P],
+    "lb_dp_status": [_P],
+    "lb_dp_adamw": [_P, _P, _P, _P, _P, _P, _P, _L, _L, _I, _I, ctypes.c_uint, _F, _F, _F, _F, _F, _F, _F, _F, _I, _P],
     "lb_flash_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _P],
     "lb_flash_fwd_tc": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _P],
     "lb_flash_status": [_P],

@@ -18,6 +18,8 @@ Expert parameters use their own replica group (dp/ep x cp).
 from __future__ import annotations
 
 import math
+import os
+import ctypes
 from contextlib import contextmanager
 from typing import Dict, List, Optional
 
@@ -53,9 +55,11 @@ def arrange_parameters(model: nn.Module) -> List[nn.Parameter]:
 
 
 @torch.no_grad()
-def build_arena(model: nn.Module, n_dense: int, n_expert: int, dtype: Optional[torch.dtype] = None):
+def build_arena(model: nn.Module, n_dense: int, n_expert: int, dtype: Optional[torch.dtype] = None, allocator=None):
     """Lay parameters out in a flat arena: [dense region | expert region], every region padded
-    so that it splits evenly (and 128-element aligned) over its replica group."""
+    so that it splits evenly (and 128-element aligned) over its replica group.
+    ``allocator(total_elements, dtype, device) -> (params, grads)`` lets the caller place both
+    arenas in peer-visible (symmetric) memory."""
     params = arrange_parameters(model)
     dtype = dtype or params[0].dtype
     device = params[0].device
@@ -76,8 +80,11 @@ def build_arena(model: nn.Module, n_dense: int, n_expert: int, dtype: Optional[t
     else:
         pad = _ALIGN * n_expert
         total = (total + pad - 1) // pad * pad
-    flat = torch.zeros(total, dtype=dtype, device=device)
-    grads = torch.zeros(total, dtype=dtype, device=device)
+    if allocator is not None:
+        flat, grads = allocator(total, dtype, device)
+    else:
+        flat = torch.zeros(total, dtype=dtype, device=device)
+        grads = torch.zeros(total, dtype=dtype, device=device)
     for p, off in zip(params, offs):
         view = flat[off:off + p.numel()].view(p.shape)
         view.copy_(p.data.to(dtype))
@@ -100,7 +107,19 @@ class DistributedAdamW:
         ctx = self.ctx
         n_dense = comm.group_size(ctx.dpcp_group)
         n_expert = comm.group_size(ctx.edpcp_group)
-        flat, grads, dense_end, offs = build_arena(model, n_dense, n_expert, param_dtype)
+        # One kernel for reduce-scatter + AdamW + all-gather over NVLink peer memory when the
+        # replica group allows it (arenas then live in symmetric memory).
+        self.fused_dp = None
+        allocator = None
+        first = next(model.parameters())
+        want_dtype = param_dtype or first.dtype
+        has_expert = any(getattr(p, "is_expert", False) for p in model.parameters())
+        if (first.is_cuda and want_dtype == torch.bfloat16 and n_dense > 1 and n_dense <= 8 and not has_expert
+                and grad_clip <= 0 and native.available() and os.environ.get("LIGHTRON_FUSED_DP", "1") != "0"
+                and dist.get_backend(ctx.dpcp_group) == "nccl"):
+            allocator = self._symmetric_allocator
+            bucket_mb = float("inf")          # a single shard range: one launch per step
+        flat, grads, dense_end, offs = build_arena(model, n_dense, n_expert, param_dtype, allocator)
         self.flat_params, self.flat_grads = flat, grads
         self.params = arrange_parameters(model)
         self.device = flat.device
@@ -115,7 +134,8 @@ class DistributedAdamW:
             if hi <= lo:
                 continue
             unit = _ALIGN * n
-            target = max(unit, int(bucket_mb * (1 << 20) / flat.element_size()) // unit * unit)
+            target = hi - lo if bucket_mb == float("inf") else \
+                max(unit, int(bucket_mb * (1 << 20) / flat.element_size()) // unit * unit)
             s = lo
             while s < hi:
                 e = min(hi, s + target)
@@ -136,7 +156,7 @@ class DistributedAdamW:
         self.param_shard = torch.empty(shard_off, dtype=flat.dtype, device=self.device)
         # ---- hooks for overlapped reduction ----
         self.sync_enabled = True
-        self.overlap = overlap and flat.is_cuda and any(b.n > 1 for b in self.buckets)
+        self.overlap = overlap and flat.is_cuda and any(b.n > 1 for b in self.buckets) and self.fused_dp is None
         self.comm_stream = torch.cuda.Stream() if self.overlap else None
         for p, off in zip(self.params, offs):
             for b in self.buckets:          # a tensor that straddles a bucket boundary counts in both
@@ -150,6 +170,27 @@ class DistributedAdamW:
         self.sp_partial = [p for n_, p in model.named_parameters()
                            if getattr(getattr(model, "args", None), "sequence_parallel", False)
                            and ctx.tp_size > 1 and p.dim() == 1]
+
+    # ---- peer-memory arenas for the fused reduce-scatter + AdamW + all-gather kernel -----------
+    def _symmetric_allocator(self, total: int, dtype, device):
+        import torch.distributed._symmetric_memory as symm_mem
+        group = self.ctx.dpcp_group
+        head = 4096                                       # flag words live in front of the arenas
+        nbytes = head + 2 * total * 2
+        buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        buf.zero_()
+        hdl = symm_mem.rendezvous(buf, group=group)
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+        ptrs = [int(x) + int(getattr(hdl, 'offset', 0)) for x in hdl.buffer_ptrs]
+        n = dist.get_world_size(group)
+        mk = lambda off: (ctypes.c_void_p * n)(*[p + off for p in ptrs])
+        flat = buf[head:head + total * 2].view(dtype)
+        grads = buf[head + total * 2:head + 4 * total].view(dtype)
+        self.fused_dp = {"buf": buf, "hdl": hdl, "flags": mk(0), "params": mk(head), "grads": mk(head + total * 2),
+                         "counter": torch.zeros(1, dtype=torch.int32, device=device), "epoch": 0,
+                         "rank": dist.get_rank(group), "n": n}
+        return flat, grads
 
     # ---- gradient synchronisation ---------------------------------------------------------
     def _reset_buckets(self):
@@ -211,6 +252,8 @@ class DistributedAdamW:
             for p in self.sp_partial:
                 p.grad.copy_(buf[off:off + p.numel()].view_as(p.grad))
                 off += p.numel()
+        if self.fused_dp is not None:
+            return
         for b in self.buckets:
             self._launch_reduce(b, async_op=False)
         for b in self.buckets:
@@ -241,6 +284,15 @@ class DistributedAdamW:
         bc1 = 1.0 - b1 ** self.step_count
         bc2 = 1.0 - b2 ** self.step_count
         n = self.shard_numel
+        if self.fused_dp is not None:
+            f, b = self.fused_dp, self.buckets[0]
+            f["epoch"] += 1
+            native.call("lb_dp_adamw", f["grads"], f["params"], f["flags"], f["counter"].data_ptr(),
+                        self.master.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
+                        b.start + f["rank"] * b.shard_len, b.shard_len, f["n"], f["rank"], f["epoch"], self.lr, b1, b2,
+                        self.eps, self.weight_decay, bc1, bc2, scale, 148 * 8, native.stream_ptr())
+            self._reset_buckets()
+            return
         if self.native:
             native.call("lb_adamw", self.master.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
                         self.grad_shard.data_ptr(), self.param_shard.data_ptr(), n, self.lr, b1, b2, self.eps,

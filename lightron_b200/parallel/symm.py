@@ -71,7 +71,8 @@ class Workspace:
         self.buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
         self.buf[: self.data_off].zero_()
         self.hdl = symm_mem.rendezvous(self.buf, group=group)
-        self.ptrs: List[int] = [int(p) for p in self.hdl.buffer_ptrs]
+        off = int(getattr(self.hdl, "offset", 0))          # the tensor may sit inside a larger symmetric block
+        self.ptrs: List[int] = [int(p) + off for p in self.hdl.buffer_ptrs]
         torch.cuda.synchronize()
         dist.barrier(group=group)            # everybody's counters are zero before anybody pushes
         self.keep_calls = 0

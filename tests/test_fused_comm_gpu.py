@@ -81,3 +81,63 @@ def test_fused_ag_gemm_and_gemm_rs(tmp_path):
                         "--master-addr", "127.0.0.1", "--master-port", "29541", str(script)], env=env,
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "FUSED_COMM_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+DP_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO"])
+from lightron_b200 import mesh
+from lightron_b200.config import ModelArgs
+from lightron_b200.models import LightronTransformer, init_weights
+from lightron_b200.optim import DistributedAdamW
+world = int(os.environ["WORLD_SIZE"])
+ctx = mesh.setup_distributed(dp_size=world)
+dev = ctx.device
+args = ModelArgs(dim=256, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=1024, intermediate_size=512, max_seq_len=128)
+finals = []
+for fused in ("1", "0"):
+    os.environ["LIGHTRON_FUSED_DP"] = fused
+    m = LightronTransformer(args, ctx, dtype=torch.bfloat16, device=dev)
+    init_weights(m, 3)
+    opt = DistributedAdamW(m, lr=1e-3, ctx=ctx)
+    assert (opt.fused_dp is not None) == (fused == "1")
+    g = torch.Generator().manual_seed(100 + ctx.rank)
+    for step in range(3):
+        tok = torch.randint(0, 1024, (2, 128), generator=g).to(dev)
+        opt.zero_grad()
+        loss = m.loss(tok, torch.roll(tok, -1, 1))
+        loss.backward()
+        gbad = int(torch.isnan(opt.flat_grads.float()).sum())
+        opt.step()
+        torch.cuda.synchronize()
+        pbad = int(torch.isnan(opt.flat_params.float()).sum())
+        print(f"[rank {ctx.rank}] fused={fused} step {step} loss {loss.item():.4f} nan grads {gbad} nan params {pbad} "
+              f"nan master {int(torch.isnan(opt.master).sum())}", flush=True)
+    torch.cuda.synchronize()
+    finals.append(opt.flat_params.float().clone())
+    # replicas must hold identical parameters after the step
+    ref = finals[-1].clone(); dist.broadcast(ref, src=0)
+    if not torch.equal(ref, finals[-1]):
+        bad = (ref != finals[-1]).nonzero().flatten()
+        raise AssertionError(f"replicas diverged (fused={fused}): {bad.numel()} of {ref.numel()} elements, first {bad[:4].tolist()} "
+                             f"last {bad[-4:].tolist()}, shard_len {opt.buckets[0].shard_len}, max diff {(ref - finals[-1]).abs().max().item()}")
+import ctypes
+from lightron_b200.ops import native
+buf = (ctypes.c_uint * 4)(); native.require().lb_dp_status(ctypes.cast(buf, ctypes.c_void_p)); assert buf[0] == 0, list(buf)
+rel = ((finals[0] - finals[1]).norm() / finals[1].norm()).item()
+assert rel < 2e-3, rel
+dist.barrier()
+if ctx.rank == 0: print("FUSED_DP_OK", rel)
+mesh.destroy()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_dp_adamw_matches_nccl_path(tmp_path):
+    script = tmp_path / "dp_worker.py"
+    script.write_text(DP_WORKER)
+    env = dict(os.environ, REPO=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29542", str(script)], env=env,
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "FUSED_DP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

@@ -176,7 +176,7 @@ def test_embedding_fwd_bwd_vocab_parallel():
     assert _rel_err(w.grad, wf.grad) < 2e-2           # bf16 atomics accumulate with rounding
 
 
-@pytest.mark.parametrize("T,V", [(257, 8192), (1024, 32000)])
+@pytest.mark.parametrize("T,V", [(257, 8192), (1024, 32000), (64, 1024), (33, 264)])
 def test_cross_entropy_fwd_bwd(T, V):
     from lightron_b200.ops import functional as OF
     logits = _rand(T, V, scale=2.0, seed=1)
