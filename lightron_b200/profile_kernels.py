@@ -1,0 +1,62 @@
+"""Small, self-terminating workloads for profiling single kernels under ncu.
+
+    python -m lightron_b200.profile_kernels gemm|attn|norm
+
+Each mode launches its kernel a few times on inputs larger than L2 but well under 1 GB, prints
+CUDA-event timings and exits; capture with e.g.
+    ncu --set full --clock-control none -k regex:gemm_bf16 -s 2 -c 1 -o out python -m lightron_b200.profile_kernels gemm
+"""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+
+def _time(fn, iters=5):
+    for _ in range(2):
+        fn()
+    ts = []
+    for _ in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record(); torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    return sorted(ts)[len(ts) // 2]
+
+
+def main(mode: str) -> None:
+    from .ops import functional as OF
+    dev = torch.device("cuda", 0)
+    if mode == "gemm":
+        M, N, K = 8192, 8192, 4096
+        a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+        ms = _time(lambda: OF.gemm(a, b))
+        print(f"gemm {M}x{N}x{K}: {ms:.3f} ms  {2.0 * M * N * K / ms / 1e9:.0f} TFLOP/s")
+    elif mode == "attn":
+        B, S, hq, hkv, d = 4, 2048, 16, 4, 64
+        q = torch.randn(B, S, hq, d, device=dev, dtype=torch.bfloat16)
+        k = torch.randn(B, S, hkv, d, device=dev, dtype=torch.bfloat16)
+        v = torch.randn(B, S, hkv, d, device=dev, dtype=torch.bfloat16)
+        sc = d ** -0.5
+        o, lse = OF.flash_fwd_native(q, k, v, True, sc)
+        do = torch.randn_like(o)
+        fl = 4.0 * B * hq * S * S * d / 2
+        f = _time(lambda: OF.flash_fwd_native(q, k, v, True, sc))
+        bw = _time(lambda: OF.flash_bwd_native(q, k, v, o, lse, do, True, sc))
+        print(f"attention B{B} S{S} hq{hq} hkv{hkv} d{d}: fwd {f:.3f} ms {fl / f / 1e9:.0f} TFLOP/s, "
+              f"bwd {bw:.3f} ms {2.5 * fl / bw / 1e9:.0f} TFLOP/s")
+    elif mode == "norm":
+        rows, cols = 65536, 2048                       # 256 MiB per tensor
+        x = torch.randn(rows, cols, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        r = torch.randn(rows, cols, device=dev, dtype=torch.bfloat16)
+        w = torch.ones(cols, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        ms = _time(lambda: OF.add_rmsnorm(x, r, w, 1e-5))
+        gb = 4 * rows * cols * 2 / 1e9
+        print(f"add_rmsnorm fwd {rows}x{cols}: {ms:.3f} ms  {gb / ms * 1e3:.0f} GB/s")
+    else:
+        raise SystemExit("mode: gemm | attn | norm")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "gemm")
