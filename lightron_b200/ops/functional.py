@@ -103,8 +103,10 @@ class _Linear(torch.autograd.Function):
 
 def linear(x: torch.Tensor, *ws: torch.Tensor) -> torch.Tensor:
     """x [..., K] times one or more [n_i, K] weights -> [..., sum n_i]."""
-    if native.use_native(x):
+    if native.use_native(x) and x.shape[-1] % 8 == 0 and all(w.shape[0] % 8 == 0 for w in ws):
         return _Linear.apply(x, *ws)
+    # CPU / fp32 oracle path, and GEMMs whose widths are not multiples of 8 (a MoE router with
+    # fewer than 8 experts): TMA needs 16-byte rows, and such a GEMM is tiny anyway
     if len(ws) == 1:
         return F.linear(x, ws[0])
     return torch.cat([F.linear(x, w) for w in ws], dim=-1)

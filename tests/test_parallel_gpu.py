@@ -1,0 +1,113 @@
+"""Every parallel layout on real GPUs (NCCL + native kernels, bf16) against the single-GPU run of
+the same config and data.  Needs 2 GPUs (4 for the composed layouts); runs as torchrun children."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+WORKER = r'''
+import json, os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO"])
+from lightron_b200 import mesh
+from lightron_b200.config import parse_config
+from lightron_b200.trainer import Trainer
+raw = json.loads(os.environ["LB_CFG"])
+steps = int(os.environ["LB_STEPS"])
+tr = Trainer(parse_config(raw, env={}))
+losses = []
+for _ in range(steps):
+    loss = tr.train_step()
+    if tr.ctx.pp_size > 1:
+        dist.all_reduce(loss, group=tr.ctx.pp_group)
+    if tr.ctx.grad_replicas > 1:
+        dist.all_reduce(loss, group=tr.ctx.dpcp_group)
+        loss = loss / tr.ctx.grad_replicas
+    losses.append(float(loss))
+if tr.args.sequence_parallel and tr.ctx.tp_size > 1:
+    from lightron_b200.parallel import symm
+    symm.check_status()
+if tr.ctx.rank == 0:
+    print("LOSSES " + json.dumps(losses), flush=True)
+mesh.destroy()
+'''
+
+BASE = {
+    "distributed": {},
+    "model": {"dim": 512, "n_layers": 4, "n_heads": 8, "n_kv_heads": 4, "vocab_size": 4096, "intermediate_size": 1024},
+    "dataset": {"name": "synthetic"},
+    "training": {"micro_batch_size": 4, "gradient_accumulation_steps": 1, "seq_length": 512, "learning_rate": 1e-3,
+                 "total_steps": 3, "seed": 0, "dtype": "bf16", "log_interval": 1000},
+}
+
+
+def _run(tmp_path, world, dist_kw, train_kw=None, model_kw=None, steps=3, port=29550):
+    raw = json.loads(json.dumps(BASE))
+    raw["distributed"].update(dist_kw)
+    raw["training"].update(train_kw or {})
+    raw["model"].update(model_kw or {})
+    script = tmp_path / "w.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, REPO=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), LB_CFG=json.dumps(raw),
+               LB_STEPS=str(steps), NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), str(script)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-2500:] + r.stderr[-2500:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("LOSSES ")][-1]
+    return json.loads(line[len("LOSSES "):])
+
+
+def _check(tmp_path, world, dist_kw, train_kw=None, model_kw=None, tol=3e-2):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    dp = dist_kw.get("dp_size", 1)
+    tk = dict(train_kw or {})
+    ga = tk.get("gradient_accumulation_steps", 1)
+    single_kw = dict(tk, gradient_accumulation_steps=ga * dp)      # same global batch, same sample order
+    want = _run(tmp_path, 1, {}, single_kw, model_kw, port=29551)
+    got = _run(tmp_path, world, dist_kw, tk, model_kw, port=29552)
+    for a, b in zip(got, want):
+        assert abs(a - b) < tol * max(1.0, abs(b)), f"{got} vs {want}"
+
+
+def test_tp2_sequence_parallel_fused(tmp_path):
+    _check(tmp_path, 2, {"tp_size": 2, "sequence_parallel": True})
+
+
+def test_tp2_plain(tmp_path):
+    _check(tmp_path, 2, {"tp_size": 2})
+
+
+def test_dp2_fused_optimizer(tmp_path):
+    _check(tmp_path, 2, {"dp_size": 2})
+
+
+def test_pp2_1f1b(tmp_path):
+    _check(tmp_path, 2, {"pp_size": 2}, {"gradient_accumulation_steps": 4, "micro_batch_size": 1})
+
+
+def test_cp2_ring(tmp_path):
+    _check(tmp_path, 2, {"cp_size": 2, "cp_mode": "ring"})
+
+
+def test_cp2_ulysses(tmp_path):
+    _check(tmp_path, 2, {"cp_size": 2, "cp_mode": "ulysses"})
+
+
+def test_ep2_moe(tmp_path):
+    _check(tmp_path, 2, {"dp_size": 2, "ep_size": 2},
+           model_kw={"moe_num_experts": 4, "moe_topk": 2, "moe_layer_freq": 2, "moe_aux_loss_coef": 0.0})
+
+
+def test_tp2_dp2_fused(tmp_path):
+    _check(tmp_path, 4, {"tp_size": 2, "dp_size": 2, "sequence_parallel": True})
+
+
+def test_tp2_pp2(tmp_path):
+    _check(tmp_path, 4, {"tp_size": 2, "pp_size": 2, "sequence_parallel": True},
+           {"gradient_accumulation_steps": 4, "micro_batch_size": 1})
