@@ -63,6 +63,8 @@ class Trainer:
         self.device = ctx.device
         fused.set_fused(d.fused_comm)
         init_pp_group_manager(ctx)
+        from . import health
+        health.check_config_agreement(cfg.to_dict())        # a rank started with another JSON fails here
         self.args = build_model_args(cfg)
         self.dtype = torch.bfloat16 if t.dtype == "bf16" else torch.float32
         torch.manual_seed(t.seed)
@@ -146,7 +148,11 @@ class Trainer:
         last_loss = float("nan")
         while self.step < t.total_steps:
             self.timer.start()
+            if self.device.type == "cuda":
+                torch.cuda.nvtx.range_push(f"step {self.step + 1}")
             loss = self.train_step()
+            if self.device.type == "cuda":
+                torch.cuda.nvtx.range_pop()
             self.timer.stop()
             if self.step % t.log_interval == 0 or self.step == t.total_steps:
                 ms = self.timer.mean_ms_max_over_ranks()          # device time, MAX over ranks
@@ -159,11 +165,15 @@ class Trainer:
                 if is_log:
                     tps_wall = (self.tokens_seen - tokens0) / max(time.time() - start, 1e-9)
                     tps_dev = tokens_per_step / (ms / 1e3) if ms > 0 else float("nan")
+                    # model FLOPs: 6 N per token for the matmuls + causal attention (fwd + bwd)
+                    a = self.args
+                    flops_tok = 6.0 * a.num_params() + 6.0 * a.n_layers * a.dim * t.seq_length
+                    mfu = flops_tok * tps_dev / (ctx.world_size * 2.25e15) if ms > 0 else float("nan")
                     print(f"Step {self.step}/{t.total_steps} | Loss: {last_loss:.4f} | TPS: {tps_wall:.2f} tokens/s"
-                          f" | device TPS: {tps_dev:.2f} | step {ms:.2f} ms", flush=True)
+                          f" | device TPS: {tps_dev:.2f} | step {ms:.2f} ms | MFU {mfu * 100:.1f}%", flush=True)
                     if log_f:
                         log_f.write(json.dumps({"step": self.step, "loss": last_loss, "tokens_per_s_wall": tps_wall,
-                                                "tokens_per_s_device": tps_dev, "step_ms": ms,
+                                                "tokens_per_s_device": tps_dev, "step_ms": ms, "mfu_vs_2.25PF": mfu,
                                                 "tokens_seen": self.tokens_seen}) + "\n")
                         log_f.flush()
                 self.timer.reset()
