@@ -75,6 +75,12 @@ class ModelArgs:
             return False
         return self.moe_layer_freq <= 1 or layer_id % self.moe_layer_freq == 1
 
+    def num_active_params(self) -> int:
+        """Parameters a token actually visits (top-k experts only): the N of the 6*N*tokens rule."""
+        mlp = 3 * self.dim * self.ffn_hidden
+        n_moe = sum(1 for i in range(self.n_layers) if self.is_moe_layer(i))
+        return self.num_params() - n_moe * max(self.moe_num_experts - max(self.moe_topk, 1), 0) * mlp
+
     def num_params(self) -> int:
         d, kv = self.dim, self.n_kv_heads * self.head_dim
         attn = 2 * d * d + 2 * d * kv
@@ -145,6 +151,7 @@ class TrainingConfig:
     dtype: str = "bf16"          # "bf16" (fp32 master weights) | "fp32"
     save_interval: int = 0       # 0 = only at the end (reference behaviour, trainer.py:330-338)
     save_dir: str = "."
+    save_final: bool = True      # the reference always writes a checkpoint after the last step
     resume: Optional[str] = None
     betas: tuple = (0.9, 0.999)
     eps: float = 1e-8

@@ -167,7 +167,7 @@ class Trainer:
                     tps_dev = tokens_per_step / (ms / 1e3) if ms > 0 else float("nan")
                     # model FLOPs: 6 N per token for the matmuls + causal attention (fwd + bwd)
                     a = self.args
-                    flops_tok = 6.0 * a.num_params() + 6.0 * a.n_layers * a.dim * t.seq_length
+                    flops_tok = 6.0 * a.num_active_params() + 6.0 * a.n_layers * a.dim * t.seq_length
                     mfu = flops_tok * tps_dev / (ctx.world_size * 2.25e15) if ms > 0 else float("nan")
                     print(f"Step {self.step}/{t.total_steps} | Loss: {last_loss:.4f} | TPS: {tps_wall:.2f} tokens/s"
                           f" | device TPS: {tps_dev:.2f} | step {ms:.2f} ms | MFU {mfu * 100:.1f}%", flush=True)
@@ -179,7 +179,7 @@ class Trainer:
                 self.timer.reset()
             if t.save_interval and self.step % t.save_interval == 0 and self.step < t.total_steps:
                 self.save()
-        path = self.save() if t.total_steps > first_step or not t.resume else None
+        path = self.save() if (t.save_final and (t.total_steps > first_step or not t.resume)) else None
         if is_log:
             print("Training Finished!", flush=True)
         if log_f:
