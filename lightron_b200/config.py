@@ -41,7 +41,7 @@ class ModelArgs:
     moe_aux_loss_coef: float = 0.01
     ep_size: int = 1
     sequence_parallel: bool = False
-    cp_mode: str = "ring"                     # "ring" (zig-zag causal) | "ulysses"
+    cp_mode: str = "ring"                     # "ring" | "allgather" (both zig-zag causal) | "ulysses"
 
     def __post_init__(self):
         if self.n_kv_heads is None:
@@ -50,8 +50,8 @@ class ModelArgs:
             raise ValueError(f"dim {self.dim} not divisible by n_heads {self.n_heads}")
         if self.n_heads % self.n_kv_heads:
             raise ValueError("n_heads must be a multiple of n_kv_heads")
-        if self.cp_mode not in ("ring", "ulysses"):
-            raise ValueError(f"cp_mode must be ring|ulysses, got {self.cp_mode}")
+        if self.cp_mode not in ("ring", "ulysses", "allgather"):
+            raise ValueError(f"cp_mode must be ring|ulysses|allgather, got {self.cp_mode}")
 
     @property
     def head_dim(self) -> int:

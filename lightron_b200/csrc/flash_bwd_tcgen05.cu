@@ -39,6 +39,7 @@ struct FaBwdParams {
   float scale;
   int causal;
   int debug;
+  int kv_brows;   // rows between consecutive batches in the K/V tensor maps (>= Sk)
 };
 
 template <int D>
@@ -188,8 +189,8 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       mbar_expect_tx(kv_full, 2 * C::TILE_BYTES);
 #pragma unroll
       for (int a = 0; a < C::ATOMS; a++) {
-        tma_load_2d(sbase + C::OFF_K + a * C::ATOM_BYTES, &tk, hk * D + a * 64, b * p.Sk + n0, kv_full);
-        tma_load_2d(sbase + C::OFF_V + a * C::ATOM_BYTES, &tv, hk * D + a * 64, b * p.Sk + n0, kv_full);
+        tma_load_2d(sbase + C::OFF_K + a * C::ATOM_BYTES, &tk, hk * D + a * 64, b * p.kv_brows + n0, kv_full);
+        tma_load_2d(sbase + C::OFF_V + a * C::ATOM_BYTES, &tv, hk * D + a * 64, b * p.kv_brows + n0, kv_full);
       }
       bool ok = true;
       for (int it = 0; it < total_it; it++) {
@@ -444,8 +445,9 @@ int launch_fa_bwd(const void* q, const void* k, const void* v, const FaBwdParams
   CUtensorMap tq, tk, tv, tdo;
   int rc;
   if ((rc = make_map_bf16(&tq, q, (uint64_t)p.hq * D, (uint64_t)p.B * p.Sq, (uint64_t)q_ts, 64, 128))) return rc;
-  if ((rc = make_map_bf16(&tk, k, (uint64_t)p.hkv * D, (uint64_t)p.B * p.Sk, (uint64_t)k_ts, 64, 128))) return rc;
-  if ((rc = make_map_bf16(&tv, v, (uint64_t)p.hkv * D, (uint64_t)p.B * p.Sk, (uint64_t)v_ts, 64, 128))) return rc;
+  const uint64_t kv_rows = (uint64_t)(p.B - 1) * p.kv_brows + p.Sk;
+  if ((rc = make_map_bf16(&tk, k, (uint64_t)p.hkv * D, kv_rows, (uint64_t)k_ts, 64, 128))) return rc;
+  if ((rc = make_map_bf16(&tv, v, (uint64_t)p.hkv * D, kv_rows, (uint64_t)v_ts, 64, 128))) return rc;
   if ((rc = make_map_bf16(&tdo, p.dout, (uint64_t)p.hq * D, (uint64_t)p.B * p.Sq, (uint64_t)p.do_ts, 64, 128))) return rc;
   static bool attr = false;
   if (!attr) {
@@ -480,7 +482,7 @@ extern "C" int lb_flash_bwd_status(void* out) {
 // Same contract as lb_flash_bwd (flash_attn.cu) except for the scratch: dq_acc is zero-initialised
 // fp32 of B * hq * ceil(Sq/128) * 128 * d elements (tile-permuted layout, see fa_dq_convert_kernel);
 // delta is fp32 scratch [B, hq, Sq].  head_dim 64 or 128; causal needs Sk >= Sq.
-extern "C" int lb_flash_bwd_tc(const void* q, const void* k, const void* v, const void* o, const void* dout,
+static int flash_bwd_tc_impl(int kv_brows, const void* q, const void* k, const void* v, const void* o, const void* dout,
                                const void* lse, void* delta, void* dq_acc, void* dq, void* dk, void* dv, int B, int Sq,
                                int Sk, int hq, int hkv, int d, long long q_ts, long long k_ts, long long v_ts,
                                long long o_ts, long long do_ts, long long dq_ts, long long dk_ts, long long dv_ts,
@@ -492,11 +494,32 @@ extern "C" int lb_flash_bwd_tc(const void* q, const void* k, const void* v, cons
     return LB_ERR_ARG;
   FaBwdParams p{(const bf16*)o, (const bf16*)dout, (const float*)lse, (float*)delta, (float*)dq_acc,
                 (bf16*)dq, (bf16*)dk, (bf16*)dv, B, Sq, Sk, hq, hkv, o_ts, do_ts, dq_ts, dk_ts, dv_ts, scale, causal,
-                getenv("LB_FA_DEBUG") ? atoi(getenv("LB_FA_DEBUG")) : 0};
+                0, kv_brows};
   cudaStream_t s = (cudaStream_t)stream;
   switch (d) {
     case 64: return launch_fa_bwd<64>(q, k, v, p, q_ts, k_ts, v_ts, s);
     case 128: return launch_fa_bwd<128>(q, k, v, p, q_ts, k_ts, v_ts, s);
     default: return LB_ERR_SHAPE;
   }
+}
+
+extern "C" int lb_flash_bwd_tc(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                               const void* lse, void* delta, void* dq_acc, void* dq, void* dk, void* dv, int B, int Sq,
+                               int Sk, int hq, int hkv, int d, long long q_ts, long long k_ts, long long v_ts,
+                               long long o_ts, long long do_ts, long long dq_ts, long long dk_ts, long long dv_ts,
+                               float scale, int causal, void* stream) {
+  return flash_bwd_tc_impl(Sk, q, k, v, o, dout, lse, delta, dq_acc, dq, dk, dv, B, Sq, Sk, hq, hkv, d, q_ts, k_ts, v_ts,
+                           o_ts, do_ts, dq_ts, dk_ts, dv_ts, scale, causal, stream);
+}
+
+// Same, for K/V that are the first Sk rows of every batch of a longer buffer (kv_brows rows per
+// batch): the context-parallel gather buffers.  dk / dv stay [B, Sk, hkv, d].
+extern "C" int lb_flash_bwd_cp(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                               const void* lse, void* delta, void* dq_acc, void* dq, void* dk, void* dv, int B, int Sq,
+                               int Sk, int kv_brows, int hq, int hkv, int d, long long q_ts, long long k_ts,
+                               long long v_ts, long long o_ts, long long do_ts, long long dq_ts, long long dk_ts,
+                               long long dv_ts, float scale, int causal, void* stream) {
+  if (kv_brows < Sk) return LB_ERR_SHAPE;
+  return flash_bwd_tc_impl(kv_brows, q, k, v, o, dout, lse, delta, dq_acc, dq, dk, dv, B, Sq, Sk, hq, hkv, d, q_ts, k_ts,
+                           v_ts, o_ts, do_ts, dq_ts, dk_ts, dv_ts, scale, causal, stream);
 }

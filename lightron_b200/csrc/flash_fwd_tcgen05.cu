@@ -12,6 +12,7 @@
 // softmax of tile 0, warps 6-9 softmax of tile 1.  While one tile is in softmax the tensor pipe
 // works on the other.  Layout / masking conventions are those of flash_attn.cu.
 // All waits are bounded; on expiry a status word is set and the CTA drains and frees its TMEM.
+#include <string.h>
 #include "tcgen05.cuh"
 
 static __device__ unsigned int g_fa_status[4] = {0, 0, 0, 0};
@@ -19,6 +20,21 @@ static __device__ unsigned int g_fa_status[4] = {0, 0, 0, 0};
 namespace {
 using namespace bw;
 
+// Context-parallel extension ("all-gather KV inside the attention kernel"): the K/V operand is a
+// gather buffer [B, S_full, hkv*d] in peer-visible memory that every rank of the CP group fills
+// by PUSHING its own zig-zag chunks (rank r owns sequence chunks r and 2c-1-r) with coalesced
+// peer stores from `n_mov` mover CTAs of this same kernel, counting each 128-key block in the
+// destination's flag word.  The attention CTAs gate every 128-key block on its flag, so the
+// exchange overlaps the softmax / MMA work on blocks that have already arrived.
+constexpr int FA_MAX_RANKS = 8;
+struct FaPush {
+  int n_mov, n_ranks, rank, chunk_rows, row_elems;   // row_elems = hkv * d
+  const bf16 *k_src, *v_src;                         // this rank's [B, 2*chunk_rows, hkv, d], token strides below
+  long long k_ts, v_ts;
+  bf16* k_dst[FA_MAX_RANKS];                         // rank r's gather buffers [B, S_full, hkv*d]
+  bf16* v_dst[FA_MAX_RANKS];
+  unsigned int* flags[FA_MAX_RANKS];                 // rank r's block counters [B][S_full / 128]
+};
 struct FaFwdParams {
   bf16* o;
   float* lse;
@@ -26,7 +42,32 @@ struct FaFwdParams {
   long long o_ts;
   float scale;
   int causal;
+  int kv_brows;                  // rows between consecutive batches in the K/V tensor maps (>= Sk)
+  const unsigned int* kv_flags;  // null, or this rank's block counters [B][kv_brows / 128]
+  unsigned int flag_target;
+  int tiles_x;                   // query tiles (256 rows) per (batch, head)
 };
+
+__device__ __forceinline__ unsigned int fa_ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long fa_globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// bounded (~20 s) wait for a peer's pushes
+__device__ __forceinline__ bool fa_flag_wait(const unsigned int* f, unsigned int target) {
+  if ((int)(fa_ld_acquire_sys(f) - target) >= 0) return true;
+  const unsigned long long t0 = fa_globaltimer();
+  while ((int)(fa_ld_acquire_sys(f) - target) < 0) {
+    __nanosleep(100);
+    if (fa_globaltimer() - t0 > 20ull * 1000ull * 1000ull * 1000ull) return false;
+  }
+  return true;
+}
 
 template <int D>
 struct FaCfg {
@@ -49,8 +90,47 @@ struct FaCfg {
 template <int D>
 __global__ void __launch_bounds__(320, 1)
 fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
-                 const __grid_constant__ CUtensorMap tv, const FaFwdParams p) {
+                 const __grid_constant__ CUtensorMap tv, const FaFwdParams p, const FaPush push) {
   using C = FaCfg<D>;
+  if ((int)blockIdx.x < push.n_mov) {
+    // ------------------------------- K/V mover CTAs -------------------------------
+    // unit = (destination rank, batch, which of this rank's two chunks, 128-row block, K or V)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int bpc = push.chunk_rows / 128;
+    const int fpb = (2 * push.n_ranks * push.chunk_rows) / 128;       // flag words per batch
+    const int units = push.n_ranks * p.B * 2 * bpc * 2;
+    const int vec_per_row = push.row_elems / 8;
+    for (int u = blockIdx.x; u < units; u += push.n_mov) {
+      int t = u;
+      const int kv = t & 1; t >>= 1;
+      const int blk = t % bpc; t /= bpc;
+      const int half = t & 1; t >>= 1;
+      const int b = t % p.B; t /= p.B;
+      const int dst = (push.rank + 1 + t) % push.n_ranks;
+      const int chunk = half ? 2 * push.n_ranks - 1 - push.rank : push.rank;
+      const long long lrow0 = (long long)b * 2 * push.chunk_rows + half * push.chunk_rows + blk * 128;
+      const long long grow0 = (long long)b * fpb * 128 + (long long)chunk * push.chunk_rows + blk * 128;
+      const bf16* src = kv ? push.v_src : push.k_src;
+      const long long ts = kv ? push.v_ts : push.k_ts;
+      bf16* dstp = (kv ? push.v_dst[dst] : push.k_dst[dst]) + grow0 * push.row_elems;
+      for (int r = warp; r < 128; r += nwarps) {
+        const uint4* sp = reinterpret_cast<const uint4*>(src + (lrow0 + r) * ts);
+        uint4* dp = reinterpret_cast<uint4*>(dstp + (long long)r * push.row_elems);
+        for (int v0 = 0; v0 < vec_per_row; v0 += 128) {
+          uint4 a[4];
+#pragma unroll
+          for (int j = 0; j < 4; j++) if (v0 + j * 32 + lane < vec_per_row) a[j] = sp[v0 + j * 32 + lane];
+#pragma unroll
+          for (int j = 0; j < 4; j++) if (v0 + j * 32 + lane < vec_per_row) dp[v0 + j * 32 + lane] = a[j];
+        }
+      }
+      __threadfence_system();
+      __syncwarp();
+      if (lane == 0)
+        asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(push.flags[dst] + (grow0 >> 7)), "r"(1u) : "memory");
+    }
+    return;
+  }
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
@@ -72,8 +152,11 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   auto pv_done = [&](int t) { return bar1 + 8u * (4 + t); };
   auto s_free = [&](int t) { return bar1 + 8u * (6 + t); };
 
-  const int mblk = gridDim.x - 1 - blockIdx.x;   // late (long) causal rows first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // 1-D grid: movers first (they must be resident before anything waits for data), then the
+  // (query tile, head, batch) CTAs with the tile index fastest
+  const int cid = (int)blockIdx.x - push.n_mov;
+  const int mblk = p.tiles_x - 1 - cid % p.tiles_x;   // late (long) causal rows first
+  const int h = (cid / p.tiles_x) % p.hq, b = cid / (p.tiles_x * p.hq);
   const int hk = h / (p.hq / p.hkv);
   const int m0 = mblk * 2 * C::BM;
   const int off = p.Sk - p.Sq;
@@ -118,17 +201,23 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       for (int j = 0; j < nb_max && ok; j++) {
         const int ks = j % C::KS, vs = j % C::VS;
         if (!mbar_wait(k_empty(ks), (((uint32_t)(j / C::KS)) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        if (p.kv_flags) {
+          // this 128-key block is pushed by its owner: wait for its counter, then order the
+          // peer's generic-proxy writes before the TMA (async proxy) reads
+          if (!fa_flag_wait(p.kv_flags + (long long)b * (p.kv_brows >> 7) + j, p.flag_target)) { *abort_flag = 1; ok = false; break; }
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         mbar_expect_tx(k_full(ks), C::TILE_BYTES);
 #pragma unroll
         for (int a = 0; a < C::ATOMS; a++)
           tma_load_2d(sbase + C::OFF_K + ks * C::TILE_BYTES + a * C::ATOM_BYTES, &tk, hk * D + a * 64,
-                      b * p.Sk + j * C::BN, k_full(ks));
+                      b * p.kv_brows + j * C::BN, k_full(ks));
         if (!mbar_wait(v_empty(vs), (((uint32_t)(j / C::VS)) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         mbar_expect_tx(v_full(vs), C::TILE_BYTES);
 #pragma unroll
         for (int a = 0; a < C::ATOMS; a++)
           tma_load_2d(sbase + C::OFF_V + vs * C::TILE_BYTES + a * C::ATOM_BYTES, &tv, hk * D + a * 64,
-                      b * p.Sk + j * C::BN, v_full(vs));
+                      b * p.kv_brows + j * C::BN, v_full(vs));
       }
       if (!ok) atomicExch(&g_fa_status[0], 1u);
     }
@@ -329,21 +418,24 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 }
 
 template <int D>
-int launch_fa_fwd(const void* q, const void* k, const void* v, const FaFwdParams& p, long long q_ts, long long k_ts,
-                  long long v_ts, cudaStream_t s) {
+int launch_fa_fwd(const void* q, const void* k, const void* v, FaFwdParams p, const FaPush& push, long long q_ts,
+                  long long k_ts, long long v_ts, cudaStream_t s) {
   using C = FaCfg<D>;
   CUtensorMap tq, tk, tv;
   int rc;
+  const uint64_t kv_rows = (uint64_t)(p.B - 1) * p.kv_brows + p.Sk;
   if ((rc = make_map_bf16(&tq, q, (uint64_t)p.hq * D, (uint64_t)p.B * p.Sq, (uint64_t)q_ts, 64, 128))) return rc;
-  if ((rc = make_map_bf16(&tk, k, (uint64_t)p.hkv * D, (uint64_t)p.B * p.Sk, (uint64_t)k_ts, 64, 128))) return rc;
-  if ((rc = make_map_bf16(&tv, v, (uint64_t)p.hkv * D, (uint64_t)p.B * p.Sk, (uint64_t)v_ts, 64, 128))) return rc;
+  if ((rc = make_map_bf16(&tk, k, (uint64_t)p.hkv * D, kv_rows, (uint64_t)k_ts, 64, 128))) return rc;
+  if ((rc = make_map_bf16(&tv, v, (uint64_t)p.hkv * D, kv_rows, (uint64_t)v_ts, 64, 128))) return rc;
   static bool attr = false;
   if (!attr) {
     cudaFuncSetAttribute(fa_fwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
     attr = true;
   }
-  dim3 grid((p.Sq + 255) / 256, p.hq, p.B);
-  fa_fwd_tc_kernel<D><<<grid, 320, C::SMEM, s>>>(tq, tk, tv, p);
+  p.tiles_x = (p.Sq + 255) / 256;
+  const long long grid = (long long)push.n_mov + (long long)p.tiles_x * p.hq * p.B;
+  if (grid > 2147483647LL) return LB_ERR_SHAPE;
+  fa_fwd_tc_kernel<D><<<(unsigned)grid, 320, C::SMEM, s>>>(tq, tk, tv, p, push);
   LB_CHECK_LAUNCH();
   return LB_OK;
 }
@@ -368,11 +460,50 @@ extern "C" int lb_flash_fwd_tc(const void* q, const void* k, const void* v, void
   if ((q_ts | k_ts | v_ts | o_ts) % 8) return LB_ERR_SHAPE;
   if (causal && Sk < Sq) return LB_ERR_SHAPE;
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o) & 15) return LB_ERR_ARG;
-  FaFwdParams p{(bf16*)o, (float*)lse, B, Sq, Sk, hq, hkv, o_ts, scale, causal};
+  FaFwdParams p{(bf16*)o, (float*)lse, B, Sq, Sk, hq, hkv, o_ts, scale, causal, Sk, nullptr, 0u, 0};
+  FaPush push;
+  memset(&push, 0, sizeof(push));
   cudaStream_t s = (cudaStream_t)stream;
   switch (d) {
-    case 64: return launch_fa_fwd<64>(q, k, v, p, q_ts, k_ts, v_ts, s);
-    case 128: return launch_fa_fwd<128>(q, k, v, p, q_ts, k_ts, v_ts, s);
+    case 64: return launch_fa_fwd<64>(q, k, v, p, push, q_ts, k_ts, v_ts, s);
+    case 128: return launch_fa_fwd<128>(q, k, v, p, push, q_ts, k_ts, v_ts, s);
+    default: return LB_ERR_SHAPE;
+  }
+}
+
+// Context-parallel forward: attention of q [B, Sq, hq, d] over the first Sk keys of the gather
+// buffers kg / vg ([B, S_full, hkv*d] contiguous, this rank's peer-visible buffers), each 128-key
+// block gated on `flags` [B][S_full/128] reaching `flag_target`.  With n_mov > 0 the same launch
+// also pushes this rank's two zig-zag chunks of k_src / v_src ([B, 2*chunk_rows, hkv, d]) into
+// every rank's buffers (kdst / vdst / flag_ptrs: host arrays of n_ranks pointers).
+// chunk_rows must be a multiple of 128; S_full = 2 * n_ranks * chunk_rows.
+extern "C" int lb_flash_fwd_cp(const void* q, const void* kg, const void* vg, void* o, void* lse, int B, int Sq, int Sk,
+                               int S_full, int hq, int hkv, int d, long long q_ts, long long o_ts, float scale,
+                               int causal, const void* flags, unsigned int flag_target, int n_mov, const void* k_src,
+                               const void* v_src, long long k_ts, long long v_ts, int n_ranks, int rank,
+                               void* const* kdst, void* const* vdst, void* const* flag_ptrs, int chunk_rows,
+                               void* stream) {
+  if (B <= 0 || Sq <= 0 || Sk <= 0 || Sk > S_full || hq % hkv || (S_full % 128)) return LB_ERR_SHAPE;
+  if ((q_ts | o_ts) % 8) return LB_ERR_SHAPE;
+  if (causal && Sk < Sq) return LB_ERR_SHAPE;
+  FaFwdParams p{(bf16*)o, (float*)lse, B, Sq, Sk, hq, hkv, o_ts, scale, causal, S_full, (const unsigned int*)flags,
+                flag_target, 0};
+  FaPush push;
+  memset(&push, 0, sizeof(push));
+  if (n_mov > 0) {
+    if (n_ranks < 1 || n_ranks > FA_MAX_RANKS || (chunk_rows % 128) || S_full != 2 * n_ranks * chunk_rows) return LB_ERR_SHAPE;
+    if ((k_ts | v_ts) % 8) return LB_ERR_SHAPE;
+    push.n_mov = n_mov; push.n_ranks = n_ranks; push.rank = rank; push.chunk_rows = chunk_rows; push.row_elems = hkv * d;
+    push.k_src = (const bf16*)k_src; push.v_src = (const bf16*)v_src; push.k_ts = k_ts; push.v_ts = v_ts;
+    for (int r = 0; r < n_ranks; r++) {
+      push.k_dst[r] = (bf16*)kdst[r]; push.v_dst[r] = (bf16*)vdst[r]; push.flags[r] = (unsigned int*)flag_ptrs[r];
+    }
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long kts = (long long)hkv * d;
+  switch (d) {
+    case 64: return launch_fa_fwd<64>(q, kg, vg, p, push, q_ts, kts, kts, s);
+    case 128: return launch_fa_fwd<128>(q, kg, vg, p, push, q_ts, kts, kts, s);
     default: return LB_ERR_SHAPE;
   }
 }

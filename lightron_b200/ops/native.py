@@ -50,6 +50,10 @@ _SIGNATURES = {
     "lb_flash_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _P],
     "lb_flash_fwd_tc": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _P],
     "lb_flash_status": [_P],
+    "lb_flash_fwd_cp": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _L, _F, _I, _P, ctypes.c_uint, _I, _P, _P,
+                        _L, _L, _I, _I, _P, _P, _P, _I, _P],
+    "lb_flash_bwd_cp": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
+                        _L, _L, _L, _L, _L, _L, _L, _L, _F, _I, _P],
     "lb_flash_bwd_status": [_P],
     "lb_flash_bwd_tc": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
                         _L, _L, _L, _L, _L, _L, _L, _L, _F, _I, _P],

@@ -231,6 +231,9 @@ def context_parallel_attention(qkv, cos, sin, positions, B, S, hq, hkv, d, group
     v = v.reshape(B, S, hkv, d).contiguous()
     if mode == "ring":
         o = ring_attention(q, k, v, group)
+    elif mode == "allgather":
+        from .cp_fused import allgather_kv_attention
+        o = allgather_kv_attention(q, k, v, group, positions=positions)
     elif mode == "ulysses":
         o = ulysses_attention(q, k, v, group)
     else:

@@ -79,7 +79,7 @@ class Trainer:
         net.train()
         self.optimizer = DistributedAdamW(net, lr=t.learning_rate, weight_decay=t.weight_decay, betas=t.betas,
                                           eps=t.eps, ctx=ctx, grad_clip=t.grad_clip)
-        cp_mode = "zigzag" if (d.cp_size > 1 and d.cp_mode == "ring") else "contiguous"
+        cp_mode = "zigzag" if (d.cp_size > 1 and d.cp_mode in ("ring", "allgather")) else "contiguous"
         self.dataloader = MicroBatchDataLoader(
             micro_batch_size=t.micro_batch_size, seq_length=t.seq_length, dataset_name=cfg.dataset.name,
             tokenizer_name=cfg.dataset.tokenizer or cfg.model.get("name"), grad_acc_steps=t.gradient_accumulation_steps,

@@ -95,7 +95,7 @@ def test_pp4_1f1b():
     _check(_cfg({"pp_size": 4}, {"gradient_accumulation_steps": 6, "micro_batch_size": 1}), 4, 2)
 
 
-@pytest.mark.parametrize("mode", ["ring", "ulysses"])
+@pytest.mark.parametrize("mode", ["ring", "ulysses", "allgather"])
 def test_cp2_gqa(mode):
     _check(_cfg({"cp_size": 2, "cp_mode": mode}, model_kw={"n_kv_heads": 2}), 2, 3)
 

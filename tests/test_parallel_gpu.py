@@ -95,6 +95,10 @@ def test_cp2_ring(tmp_path):
     _check(tmp_path, 2, {"cp_size": 2, "cp_mode": "ring"})
 
 
+def test_cp2_allgather_kv_fused(tmp_path):
+    _check(tmp_path, 2, {"cp_size": 2, "cp_mode": "allgather"})
+
+
 def test_cp2_ulysses(tmp_path):
     _check(tmp_path, 2, {"cp_size": 2, "cp_mode": "ulysses"})
 
