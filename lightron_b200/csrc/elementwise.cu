@@ -141,7 +141,7 @@ __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, bf16
 extern "C" int lb_rmsnorm_bwd_blocks(int rows, int cols) {
   (void)cols;
   int blocks = (rows + 7) / 8;
-  if (blocks > 148 * 2) blocks = 148 * 2;
+  if (blocks > 148 * 6) blocks = 148 * 6;          // 48 warps per SM: the two-pass rows need the occupancy
   return blocks < 1 ? 1 : blocks;
 }
 

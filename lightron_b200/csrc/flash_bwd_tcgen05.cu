@@ -105,24 +105,32 @@ __global__ void fa_dq_convert_kernel(const FaBwdParams p) {
   }
 }
 
+// delta[b, h, i] = sum_d o * do.  D/8 threads per (token, head), 16 bytes per thread per tensor.
 template <int D>
 __global__ void fa_delta_kernel(const FaBwdParams p) {
-  const int lane = threadIdx.x & 31;
+  constexpr int TPR = D / 8;                                   // threads per row: 8 or 16
   const long long total = (long long)p.B * p.Sq * p.hq;
-  for (long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); idx < total;
-       idx += (long long)gridDim.x * (blockDim.x >> 5)) {
-    const int h = (int)(idx % p.hq);
-    const long long bi = idx / p.hq;
-    const bf16* o = p.o + bi * p.o_ts + (long long)h * D;
-    const bf16* d = p.dout + bi * p.do_ts + (long long)h * D;
+  const int rpb = blockDim.x / TPR;                            // rows per block and iteration
+  const int sub = threadIdx.x % TPR;
+  // every thread of the block runs the same number of iterations, so the shuffles see whole warps
+  for (long long base = (long long)blockIdx.x * rpb; base < total; base += (long long)gridDim.x * rpb) {
+    const long long idx = base + threadIdx.x / TPR;
+    const bool live = idx < total;
     float s = 0.f;
-    for (int c = lane * 2; c < D; c += 64) {
-      const float2 a = __bfloat1622float2(*reinterpret_cast<const bf162*>(o + c));
-      const float2 e = __bfloat1622float2(*reinterpret_cast<const bf162*>(d + c));
-      s += a.x * e.x + a.y * e.y;
+    int h = 0;
+    long long bi = 0;
+    if (live) {
+      h = (int)(idx % p.hq);
+      bi = idx / p.hq;
+      float a[8], e[8];
+      unpack8(*reinterpret_cast<const uint4*>(p.o + bi * p.o_ts + (long long)h * D + sub * 8), a);
+      unpack8(*reinterpret_cast<const uint4*>(p.dout + bi * p.do_ts + (long long)h * D + sub * 8), e);
+#pragma unroll
+      for (int k = 0; k < 8; k++) s += a[k] * e[k];
     }
-    s = warp_sum(s);
-    if (lane == 0) {
+#pragma unroll
+    for (int o = TPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);   // whole warps stay converged
+    if (live && sub == 0) {
       const int b = (int)(bi / p.Sq), i = (int)(bi % p.Sq);
       p.delta[((long long)b * p.hq + h) * p.Sq + i] = s;
     }
@@ -455,7 +463,8 @@ int launch_fa_bwd(const void* q, const void* k, const void* v, const FaBwdParams
     attr = true;
   }
   const long long rows = (long long)p.B * p.Sq * p.hq;
-  int dblocks = (int)((rows + 7) / 8 > 148 * 8 ? 148 * 8 : (rows + 7) / 8);
+  const long long rows_per_block = 256 / (D / 8);
+  int dblocks = (int)((rows + rows_per_block - 1) / rows_per_block > 148 * 16 ? 148 * 16 : (rows + rows_per_block - 1) / rows_per_block);
   fa_delta_kernel<D><<<dblocks, 256, 0, s>>>(p);
   LB_CHECK_LAUNCH();
   dim3 grid((p.Sk + 127) / 128, p.hkv, p.B);
