@@ -129,19 +129,140 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const bf16* __restrict
     partial[(size_t)blockIdx.x * cols + j] = s_dw[(j & 7) * nvec + (j >> 3)];
 }
 
-__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, bf16* __restrict__ dw, int nblk, int cols) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= cols) return;
-  float s = 0.f;
-  for (int b = 0; b < nblk; b++) s += partial[(size_t)b * cols + j];
-  dw[j] = __float2bfloat16(s);
+// Block-per-row version (no shared-memory atomics): the block's T threads cover one row with VPT
+// uint4 each (cols = 8 * T * VPT), so a thread owns the same 8*VPT columns of every row and keeps
+// their dw partial sums in registers.  RB rows are in flight per iteration; their dy / x stay in
+// registers between the dot product (one block reduction per iteration, double-buffered so a single
+// barrier suffices) and the dx pass.
+template <int VPT, int RB>
+__global__ void __launch_bounds__(256, (VPT == 1 ? 3 : (VPT <= 3 ? 2 : 1))) rmsnorm_bwd_blk_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                              const bf16* __restrict__ w, const float* __restrict__ rstd,
+                                                              const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                                                              float* __restrict__ partial, int rows, int cols) {
+  __shared__ float s_red[2][RB][8];
+  const int T = blockDim.x, t = threadIdx.x, lane = t & 31, warp = t >> 5, nw = T >> 5;
+  const float inv_cols = 1.f / (float)cols;
+  float wf[VPT][8], acc[VPT][8];
+#pragma unroll
+  for (int k = 0; k < VPT; k++) {
+    unpack8(reinterpret_cast<const uint4*>(w)[t + T * k], wf[k]);
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[k][i] = 0.f;
+  }
+  int par = 0;
+  for (int row0 = blockIdx.x * RB; row0 < rows; row0 += gridDim.x * RB, par ^= 1) {
+    uint4 kd[RB][VPT], kx[RB][VPT];
+    float r[RB], dot[RB];
+#pragma unroll
+    for (int rb = 0; rb < RB; rb++) {
+      const int row = row0 + rb;
+      const bool ok = row < rows;
+      r[rb] = ok ? rstd[row] : 0.f;
+#pragma unroll
+      for (int k = 0; k < VPT; k++) {
+        kd[rb][k] = ok ? reinterpret_cast<const uint4*>(dy + (size_t)row * cols)[t + T * k] : make_uint4(0, 0, 0, 0);
+        kx[rb][k] = ok ? reinterpret_cast<const uint4*>(x + (size_t)row * cols)[t + T * k] : make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int rb = 0; rb < RB; rb++) {
+      float d = 0.f;
+#pragma unroll
+      for (int k = 0; k < VPT; k++) {
+        float a[8], b[8];
+        unpack8(kd[rb][k], a);
+        unpack8(kx[rb][k], b);
+#pragma unroll
+        for (int i = 0; i < 8; i++) d += a[i] * wf[k][i] * b[i];
+      }
+      d = warp_sum(d * r[rb]);
+      if (lane == 0) s_red[par][rb][warp] = d;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int rb = 0; rb < RB; rb++) {
+      float d = 0.f;
+      for (int ww = 0; ww < nw; ww++) d += s_red[par][rb][ww];
+      dot[rb] = d * inv_cols;
+    }
+#pragma unroll
+    for (int rb = 0; rb < RB; rb++) {
+      const int row = row0 + rb;
+      if (row >= rows) break;
+#pragma unroll
+      for (int k = 0; k < VPT; k++) {
+        float a[8], b[8], o[8];
+        unpack8(kd[rb][k], a);
+        unpack8(kx[rb][k], b);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const float xhat = b[i] * r[rb];
+          o[i] = r[rb] * (a[i] * wf[k][i] - xhat * dot[rb]);
+          acc[k][i] += a[i] * xhat;
+        }
+        if (dres) {
+          float e[8];
+          unpack8(reinterpret_cast<const uint4*>(dres + (size_t)row * cols)[t + T * k], e);
+#pragma unroll
+          for (int i = 0; i < 8; i++) o[i] += e[i];
+        }
+        reinterpret_cast<uint4*>(dx + (size_t)row * cols)[t + T * k] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VPT; k++) {
+    float* dst = partial + (size_t)blockIdx.x * cols + (size_t)(t + T * k) * 8;
+    *reinterpret_cast<float4*>(dst) = make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[k][4], acc[k][5], acc[k][6], acc[k][7]);
+  }
+}
+
+// Launches the block-per-row version when the width fits it (cols = 8 * T * VPT with T a multiple
+// of 32, T <= 256, VPT <= 4); returns false otherwise.
+static bool rmsnorm_bwd_blk_dispatch(const void* dy, const void* x, const void* w, const void* rstd, const void* dres,
+                                     void* dx, void* partial, int rows, int cols, int nblk, cudaStream_t s) {
+  const int nvec = cols / 8;
+  const int vpt = (nvec + 255) / 256;
+  if (vpt > 4 || nvec % vpt) return false;
+  const int T = nvec / vpt;
+  if (T % 32) return false;
+#define LB_RMS_BLK(V, R)                                                                                          \
+  rmsnorm_bwd_blk_kernel<V, R><<<nblk, T, 0, s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)rstd, \
+                                                  (const bf16*)dres, (bf16*)dx, (float*)partial, rows, cols)
+  switch (vpt) {
+    case 1: LB_RMS_BLK(1, 2); break;
+    case 2: LB_RMS_BLK(2, 2); break;
+    case 3: LB_RMS_BLK(3, 1); break;
+    default: LB_RMS_BLK(4, 1); break;
+  }
+#undef LB_RMS_BLK
+  return true;
+}
+
+// dw[j] = sum over blocks of partial[b, j]: 32 columns x 32 row lanes per block.
+__global__ void __launch_bounds__(1024) rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, bf16* __restrict__ dw,
+                                                                 int nblk, int cols) {
+  __shared__ float s[32][33];
+  const int j = blockIdx.x * 32 + threadIdx.x;
+  float v = 0.f;
+  if (j < cols)
+    for (int b = threadIdx.y; b < nblk; b += 32) v += partial[(size_t)b * cols + j];
+  s[threadIdx.y][threadIdx.x] = v;
+  __syncthreads();
+  if (threadIdx.y == 0 && j < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; k++) t += s[k][threadIdx.x];
+    dw[j] = __float2bfloat16(t);
+  }
 }
 
 // Number of blocks (= rows of the `partial` scratch) that lb_rmsnorm_bwd uses for this shape.
 extern "C" int lb_rmsnorm_bwd_blocks(int rows, int cols) {
   (void)cols;
   int blocks = (rows + 7) / 8;
-  if (blocks > 148 * 6) blocks = 148 * 6;          // 48 warps per SM: the two-pass rows need the occupancy
+  if (blocks > 148 * 4) blocks = 148 * 4;
   return blocks < 1 ? 1 : blocks;
 }
 
@@ -151,11 +272,15 @@ extern "C" int lb_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
   if (nblk != lb_rmsnorm_bwd_blocks(rows, cols)) return LB_ERR_ARG;
   cudaStream_t s = (cudaStream_t)stream;
   size_t smem = (size_t)cols * sizeof(float);
-  if (smem > 48 * 1024) cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  rmsnorm_bwd_kernel<<<nblk, 256, smem, s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)rstd,
-                                             (const bf16*)dres, (bf16*)dx, (float*)partial, rows, cols);
-  LB_CHECK_LAUNCH();
-  rmsnorm_dw_reduce_kernel<<<(cols + 255) / 256, 256, 0, s>>>((const float*)partial, (bf16*)dw, nblk, cols);
+  if (rmsnorm_bwd_blk_dispatch(dy, x, w, rstd, dres, dx, partial, rows, cols, nblk, s)) {
+    LB_CHECK_LAUNCH();
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    rmsnorm_bwd_kernel<<<nblk, 256, smem, s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)rstd,
+                                               (const bf16*)dres, (bf16*)dx, (float*)partial, rows, cols);
+    LB_CHECK_LAUNCH();
+  }
+  rmsnorm_dw_reduce_kernel<<<(cols + 31) / 32, dim3(32, 32), 0, s>>>((const float*)partial, (bf16*)dw, nblk, cols);
   LB_CHECK_LAUNCH();
   return LB_OK;
 }
@@ -573,7 +698,7 @@ extern "C" int lb_rmsnorm_bwd_static(const void* dy, const void* x, const void* 
   rmsnorm_bwd_kernel<<<nblk, 256, smem, s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)rstd,
                                              (const bf16*)dres, (bf16*)dx, partial, rows, cols);
   LB_CHECK_LAUNCH();
-  rmsnorm_dw_reduce_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial, (bf16*)dw, nblk, cols);
+  rmsnorm_dw_reduce_kernel<<<(cols + 31) / 32, dim3(32, 32), 0, s>>>(partial, (bf16*)dw, nblk, cols);
   LB_CHECK_LAUNCH();
   return LB_OK;
 }

@@ -88,7 +88,7 @@ def test_linear_autograd_fused_weights():
 # ---- elementwise ------------------------------------------------------------------------------------
 
 
-@pytest.mark.parametrize("rows,cols", [(64, 256), (1000, 2048), (333, 4096)])
+@pytest.mark.parametrize("rows,cols", [(64, 256), (1000, 2048), (333, 4096), (129, 768), (77, 6144), (50, 8192), (40, 264)])
 def test_rmsnorm_fwd_bwd(rows, cols):
     from lightron_b200.ops import functional as OF, reference as ref
     x = _rand(rows, cols, seed=1).requires_grad_(True)
