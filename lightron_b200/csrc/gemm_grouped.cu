@@ -1,0 +1,399 @@
+// Grouped bf16 GEMM for sm_100a: up to 8 independent problems  C_i[M_i,N_i] (+)= op(A_i) op(B_i)^T
+// in ONE persistent launch.
+//
+// Why: a single GEMM whose tile count is not a multiple of the SM count leaves SMs idle in its
+// last wave (a weight gradient [2560, 2048] has 160 tiles for 148 SMs: the second wave is 8 %
+// full).  Launching the data gradient and the weight gradient of a linear layer together, or
+// the GEMMs of all local experts of a MoE layer, gives the scheduler short tiles to fill those
+// holes.  The host computes a static schedule (longest tiles first, each to the least loaded
+// CTA), uploads it once per shape, and every role of a CTA walks the same list, so no
+// intra-kernel tile broadcast is needed.
+//
+// The main loop is the one of gemm_tcgen05.cu: TMA (128-byte swizzle, no multicast) -> 4-stage
+// mbarrier ring -> tcgen05.mma 128x256x16 -> two 256-column TMEM accumulators -> tcgen05.ld
+// epilogue overlapped with the next tile.  `accumulate` adds the old contents of C in the
+// epilogue (gradient accumulation over micro-batches without a separate add).
+// Every wait is bounded; on expiry the kernel records a status code (lb_gemm_grouped_status),
+// stops issuing work, frees its TMEM and returns.
+#include <cuda.h>
+#include <string.h>
+#include <algorithm>
+#include <map>
+#include <mutex>
+#include <queue>
+#include <vector>
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+static __device__ unsigned int g_grp_status[4] = {0, 0, 0, 0};
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int NUM_THREADS = 192;
+constexpr int GROUP_M = 8;
+constexpr int MAX_PROBLEMS = 8;
+
+struct Problem {
+  bf16* C;
+  long long ldc;
+  int M, N, K;
+  int a_mn, b_mn, accumulate;
+  int tiles_m, tiles_n, num_kb;
+};
+
+struct GroupedParams {
+  CUtensorMap ta[MAX_PROBLEMS];
+  CUtensorMap tb[MAX_PROBLEMS];
+  Problem prob[MAX_PROBLEMS];
+  const int* offsets;   // [grid + 1] first item of every CTA
+  const int* items;     // (problem << 24) | tile index inside the problem
+};
+
+__device__ __forceinline__ void tile_coords(int t, const Problem& p, int& tm, int& tn) {
+  const int group_size = GROUP_M * p.tiles_n;
+  const int group = t / group_size;
+  const int first_m = group * GROUP_M;
+  const int gsz = min(p.tiles_m - first_m, GROUP_M);
+  const int in_group = t - group * group_size;
+  tm = first_m + in_group % gsz;
+  tn = in_group / gsz;
+}
+
+__device__ __forceinline__ void give_up(volatile int* abort_flag, unsigned where) {
+  *abort_flag = 1;
+  atomicExch(&g_grp_status[0], 1u);
+  atomicExch(&g_grp_status[1], where);
+}
+
+// One tile of the producer / of the MMA issuer, specialised on the operand majors: with the majors
+// as compile-time constants every descriptor field and the number of TMA boxes is a constant, so the
+// single-thread issue loops stay on the uniform datapath although the tile itself comes from a list
+// in memory.
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ bool produce_tile(const CUtensorMap* ta, const CUtensorMap* tb, int m0, int n0, int num_kb,
+                                             uint32_t smem_base, uint32_t bar_base, int& stage, uint32_t& phase,
+                                             volatile int* abort_flag) {
+  for (int kb = 0; kb < num_kb; kb++) {
+    if (!bw::mbar_wait(bar_base + 8u * (STAGES + stage), phase ^ 1u, abort_flag)) return false;
+    const uint32_t fb = bar_base + 8u * stage;
+    bw::mbar_expect_tx(fb, STAGE_BYTES);
+    const uint32_t sa = smem_base + stage * STAGE_BYTES;
+    const uint32_t sb = sa + A_BYTES;
+    const int k0 = kb * BK;
+    if (!A_MN) {
+      bw::tma_load_2d(sa, ta, k0, m0, fb);                                                      // box {64 k, 128 m}
+    } else {
+#pragma unroll
+      for (int j = 0; j < BM / 64; j++) bw::tma_load_2d(sa + j * 8192, ta, m0 + 64 * j, k0, fb);  // box {64 m, 64 k}
+    }
+    if (!B_MN) {
+      bw::tma_load_2d(sb, tb, k0, n0, fb);                                                      // box {64 k, 256 n}
+    } else {
+#pragma unroll
+      for (int j = 0; j < BN / 64; j++) bw::tma_load_2d(sb + j * 8192, tb, n0 + 64 * j, k0, fb);  // box {64 n, 64 k}
+    }
+    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+  }
+  return true;
+}
+
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ bool mma_tile(uint32_t d_tmem, int num_kb, uint32_t smem_base, uint32_t bar_base, int& stage,
+                                         uint32_t& phase, volatile int* abort_flag) {
+  constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  constexpr uint32_t a_lbo = A_MN ? 8192u : 16u, b_lbo = B_MN ? 8192u : 16u;
+  constexpr uint32_t a_kstep = A_MN ? 2048u : 32u, b_kstep = B_MN ? 2048u : 32u;   // bytes per K=16 slice
+  for (int kb = 0; kb < num_kb; kb++) {
+    if (!bw::mbar_wait(bar_base + 8u * stage, phase, abort_flag)) return false;
+    bw::fence_after();
+    const uint32_t sa = smem_base + stage * STAGE_BYTES;
+    const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+    for (int k = 0; k < BK / 16; k++) {
+      const uint64_t ad = bw::make_desc(sa + k * a_kstep, a_lbo, 1024u);
+      const uint64_t bd = bw::make_desc(sb + k * b_kstep, b_lbo, 1024u);
+      bw::umma_bf16(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
+    }
+    bw::umma_commit(bar_base + 8u * (STAGES + stage));   // frees this smem stage when the MMAs have read it
+    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+  }
+  return true;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_grouped_kernel(const __grid_constant__ GroupedParams gp) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = bw::smem_u32(smem);
+  const uint32_t bar_base = bw::smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const int item_begin = gp.offsets[blockIdx.x], item_end = gp.offsets[blockIdx.x + 1];
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES; s++) {
+      bw::mbar_init(full_bar(s), 1);
+      bw::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; a++) {
+      bw::mbar_init(tfull_bar(a), 1);
+      bw::mbar_init(tempty_bar(a), 4);
+    }
+    bw::mbar_init_fence();
+  }
+  if (warp == 1) bw::tmem_alloc(bw::smem_u32(tmem_slot), 512);
+  bw::fence_before();
+  __syncthreads();
+  bw::fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int next_item = item_begin < item_end ? gp.items[item_begin] : 0;
+      for (int it = item_begin; it < item_end && ok; it++) {
+        const int item = next_item;
+        if (it + 1 < item_end) next_item = gp.items[it + 1];      // in flight while this tile streams
+        const int pi = item >> 24;
+        const CUtensorMap* ta = &gp.ta[pi];
+        const CUtensorMap* tb = &gp.tb[pi];
+        int tm, tn;
+        tile_coords(item & 0xFFFFFF, gp.prob[pi], tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        const int num_kb = gp.prob[pi].num_kb;
+        switch (gp.prob[pi].a_mn * 2 + gp.prob[pi].b_mn) {
+          case 0: ok = produce_tile<false, false>(ta, tb, m0, n0, num_kb, smem_base, bar_base, stage, phase, abort_flag); break;
+          case 1: ok = produce_tile<false, true>(ta, tb, m0, n0, num_kb, smem_base, bar_base, stage, phase, abort_flag); break;
+          case 2: ok = produce_tile<true, false>(ta, tb, m0, n0, num_kb, smem_base, bar_base, stage, phase, abort_flag); break;
+          default: ok = produce_tile<true, true>(ta, tb, m0, n0, num_kb, smem_base, bar_base, stage, phase, abort_flag); break;
+        }
+        if (!ok) give_up(abort_flag, 1u);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int n = 0;
+      int next_item = item_begin < item_end ? gp.items[item_begin] : 0;
+      for (int it = item_begin; it < item_end && ok; it++, n++) {
+        const int pi = next_item >> 24;
+        if (it + 1 < item_end) next_item = gp.items[it + 1];
+        const int num_kb = gp.prob[pi].num_kb;
+        const int majors = gp.prob[pi].a_mn * 2 + gp.prob[pi].b_mn;
+        const int acc = n & 1;
+        const uint32_t acc_phase = (uint32_t)(n >> 1) & 1u;
+        if (!bw::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { give_up(abort_flag, 2u); ok = false; break; }
+        bw::fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
+        switch (majors) {
+          case 0: ok = mma_tile<false, false>(d_tmem, num_kb, smem_base, bar_base, stage, phase, abort_flag); break;
+          case 1: ok = mma_tile<false, true>(d_tmem, num_kb, smem_base, bar_base, stage, phase, abort_flag); break;
+          case 2: ok = mma_tile<true, false>(d_tmem, num_kb, smem_base, bar_base, stage, phase, abort_flag); break;
+          default: ok = mma_tile<true, true>(d_tmem, num_kb, smem_base, bar_base, stage, phase, abort_flag); break;
+        }
+        if (ok) bw::umma_commit(tfull_bar(acc));          // accumulator complete
+        else give_up(abort_flag, 3u);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (4 warps) ------------------------------
+    const int quad = warp & 3;
+    int n = 0;
+    int next_item = item_begin < item_end ? gp.items[item_begin] : 0;
+    for (int it = item_begin; it < item_end; it++, n++) {
+      const int item = next_item;
+      if (it + 1 < item_end) next_item = gp.items[it + 1];
+      const int pi = item >> 24;
+      int tm, tn;
+      tile_coords(item & 0xFFFFFF, gp.prob[pi], tm, tn);
+      const int pM = gp.prob[pi].M, pN = gp.prob[pi].N;
+      const bool accumulate = gp.prob[pi].accumulate != 0;
+      bf16* const pC = gp.prob[pi].C;
+      const long long ldc = gp.prob[pi].ldc;
+      const int acc = n & 1;
+      const uint32_t acc_phase = (uint32_t)(n >> 1) & 1u;
+      if (!bw::mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { give_up(abort_flag, 4u); break; }
+      bw::fence_after();
+      const int row = tm * BM + quad * 32 + lane;
+      const int n0 = tn * BN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * BN;
+      bf16* crow = pC + (size_t)row * ldc + n0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c++) {
+        uint32_t r[32];
+        bw::tmem_ld32(taddr + c * 32, r);
+        bw::tmem_ld_wait();
+        if (row < pM) {
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            const int col = n0 + c * 32 + g * 8;
+            if (col < pN) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[g * 8 + i]);
+              uint4* dst = reinterpret_cast<uint4*>(crow + c * 32 + g * 8);
+              if (accumulate) {
+                float o[8];
+                unpack8(*dst, o);
+#pragma unroll
+                for (int i = 0; i < 8; i++) f[i] += o[i];
+              }
+              *dst = pack8(f);
+            }
+          }
+        }
+      }
+      bw::fence_before();
+      __syncwarp();
+      if (lane == 0) bw::mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  bw::fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    bw::fence_after();
+    bw::tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---- host side: static schedule, cached per (device, shapes) -------------------------------------
+struct Schedule {
+  int grid = 0;
+  int* d_offsets = nullptr;
+  int* d_items = nullptr;
+};
+std::map<std::vector<int>, Schedule> g_schedules;
+std::mutex g_sched_mutex;
+int g_sms = 0;
+
+// Longest tiles first, each to the least loaded CTA (ties: lowest CTA index, which keeps tiles
+// that run at the same time adjacent in the problem's L2-friendly order).
+int build_schedule(const Problem* probs, int np, int sms, Schedule* out) {
+  struct Item { int cost, code; };
+  std::vector<Item> items;
+  std::vector<int> order(np);
+  for (int i = 0; i < np; i++) order[i] = i;
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return probs[a].num_kb > probs[b].num_kb; });
+  for (int oi = 0; oi < np; oi++) {
+    const int i = order[oi];
+    const int nt = probs[i].tiles_m * probs[i].tiles_n;
+    if (nt >= (1 << 24)) return LB_ERR_SHAPE;
+    for (int t = 0; t < nt; t++) items.push_back({probs[i].num_kb + 6, (i << 24) | t});   // +6: fixed cost per tile
+  }
+  const int total = (int)items.size();
+  const int grid = total < sms ? total : sms;
+  typedef std::pair<long long, int> Load;
+  std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
+  for (int c = 0; c < grid; c++) heap.push({0, c});
+  std::vector<std::vector<int>> per(grid);
+  for (const Item& it : items) {
+    Load l = heap.top();
+    heap.pop();
+    per[l.second].push_back(it.code);
+    heap.push({l.first + it.cost, l.second});
+  }
+  std::vector<int> offsets(grid + 1, 0), flat;
+  flat.reserve(total);
+  for (int c = 0; c < grid; c++) {
+    offsets[c] = (int)flat.size();
+    flat.insert(flat.end(), per[c].begin(), per[c].end());
+  }
+  offsets[grid] = (int)flat.size();
+  if (cudaMalloc(&out->d_offsets, sizeof(int) * (grid + 1)) != cudaSuccess) return LB_ERR_LAUNCH;
+  if (cudaMalloc(&out->d_items, sizeof(int) * (total > 0 ? total : 1)) != cudaSuccess) return LB_ERR_LAUNCH;
+  cudaMemcpy(out->d_offsets, offsets.data(), sizeof(int) * (grid + 1), cudaMemcpyHostToDevice);
+  cudaMemcpy(out->d_items, flat.data(), sizeof(int) * total, cudaMemcpyHostToDevice);
+  out->grid = grid;
+  return LB_OK;
+}
+
+}  // namespace
+
+// Copies the status words of the grouped GEMM kernel to host memory and clears them.
+extern "C" int lb_gemm_grouped_status(void* out) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_grp_status, sizeof(unsigned int) * 4);
+  if (e != cudaSuccess) { g_lb_last_cuda_error = (int)e; return LB_ERR_LAUNCH; }
+  unsigned int zeros[4] = {0, 0, 0, 0};
+  cudaMemcpyToSymbol(g_grp_status, zeros, sizeof(zeros));
+  return LB_OK;
+}
+
+// n problems (1..8), arrays of length n.  Per problem the rules of lb_gemm_bf16 apply: pointers
+// 16-byte aligned, lda / ldb / ldc / N multiples of 8 (M too when a_mn).  accumulate[i] != 0 adds
+// the product to the old contents of C_i.  The first call with a new set of shapes builds and
+// uploads the schedule (two small device allocations, synchronous copies); later calls only launch.
+extern "C" int lb_gemm_grouped(int n, const void* const* A, const void* const* B, void* const* C, const int* M,
+                               const int* N, const int* K, const long long* lda, const long long* ldb,
+                               const long long* ldc, const int* a_mn, const int* b_mn, const int* accumulate,
+                               void* stream) {
+  if (n < 1 || n > MAX_PROBLEMS) return LB_ERR_SHAPE;
+  static thread_local GroupedParams gp;         // 2.5 KB of tensor maps: kept off the stack, one per calling thread
+  std::vector<int> key;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  key.push_back(dev);
+  for (int i = 0; i < n; i++) {
+    if (M[i] <= 0 || N[i] <= 0 || K[i] <= 0) return LB_ERR_SHAPE;
+    if ((lda[i] % 8) || (ldb[i] % 8) || (ldc[i] % 8) || (N[i] % 8) || (a_mn[i] && (M[i] % 8))) return LB_ERR_SHAPE;
+    if (((uintptr_t)A[i] | (uintptr_t)B[i] | (uintptr_t)C[i]) & 15) return LB_ERR_ARG;
+    int rc;
+    if (!a_mn[i]) rc = bw::make_map_bf16(&gp.ta[i], A[i], (uint64_t)K[i], (uint64_t)M[i], (uint64_t)lda[i], BK, BM);
+    else          rc = bw::make_map_bf16(&gp.ta[i], A[i], (uint64_t)M[i], (uint64_t)K[i], (uint64_t)lda[i], 64, BK);
+    if (rc) return rc;
+    if (!b_mn[i]) rc = bw::make_map_bf16(&gp.tb[i], B[i], (uint64_t)K[i], (uint64_t)N[i], (uint64_t)ldb[i], BK, BN);
+    else          rc = bw::make_map_bf16(&gp.tb[i], B[i], (uint64_t)N[i], (uint64_t)K[i], (uint64_t)ldb[i], 64, BK);
+    if (rc) return rc;
+    Problem& p = gp.prob[i];
+    p.C = (bf16*)C[i]; p.ldc = ldc[i]; p.M = M[i]; p.N = N[i]; p.K = K[i];
+    p.a_mn = a_mn[i]; p.b_mn = b_mn[i]; p.accumulate = accumulate ? accumulate[i] : 0;
+    p.tiles_m = (M[i] + BM - 1) / BM; p.tiles_n = (N[i] + BN - 1) / BN; p.num_kb = (K[i] + BK - 1) / BK;
+    key.push_back(M[i]); key.push_back(N[i]); key.push_back(K[i]);
+  }
+  {
+    std::lock_guard<std::mutex> lock(g_sched_mutex);
+    if (g_sms == 0) {
+      cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
+      cudaFuncSetAttribute(gemm_grouped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    }
+  }
+  Schedule sched;
+  {
+    std::lock_guard<std::mutex> lock(g_sched_mutex);
+    auto it = g_schedules.find(key);
+    if (it == g_schedules.end()) {
+      Schedule s;
+      int rc = build_schedule(gp.prob, n, g_sms, &s);
+      if (rc) return rc;
+      it = g_schedules.emplace(key, s).first;
+    }
+    sched = it->second;
+  }
+  gp.offsets = sched.d_offsets;
+  gp.items = sched.d_items;
+  gemm_grouped_kernel<<<sched.grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(gp);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}

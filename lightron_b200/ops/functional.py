@@ -43,7 +43,7 @@ def _as_strided_cat(ws: Sequence[torch.Tensor]) -> torch.Tensor:
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = False,
-         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+         out: Optional[torch.Tensor] = None, legacy: bool = False) -> torch.Tensor:
     """C[M,N] = A . B^T on the tcgen05 kernel.  ``a_mn``: A is stored [K, M] (M contiguous)
     instead of [M, K]; ``b_mn``: B is stored [K, N] instead of [N, K].  Row strides are free
     (multiples of 8 elements), inner stride must be 1."""
@@ -54,8 +54,41 @@ def gemm(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = Fals
     if out is None:
         out = torch.empty(M, N, dtype=a.dtype, device=a.device)
     native.call("lb_gemm_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K,
-                a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn), 0, native.stream_ptr())
+                a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn), int(legacy), native.stream_ptr())
     return out
+
+
+def gemm_grouped(problems) -> List[torch.Tensor]:
+    """Several independent GEMMs in one persistent launch (``lb_gemm_grouped``): short tiles of one
+    problem fill the idle tail of another.  ``problems``: up to 8 tuples
+    ``(a, b, a_mn, b_mn, out_or_None, accumulate)`` with the conventions of :func:`gemm`;
+    ``accumulate`` adds the product to the old contents of ``out``.  Returns the outputs."""
+    n = len(problems)
+    assert 1 <= n <= 8
+    import ctypes
+    PA, IA, LA = ctypes.c_void_p * n, ctypes.c_int * n, ctypes.c_longlong * n
+    A, B, C = PA(), PA(), PA()
+    M, N, K, amn, bmn, acc = IA(), IA(), IA(), IA(), IA(), IA()
+    lda, ldb, ldc = LA(), LA(), LA()
+    outs = []
+    for i, (a, b, a_mn, b_mn, out, accumulate) in enumerate(problems):
+        assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+        m, k = (a.shape[1], a.shape[0]) if a_mn else a.shape
+        nn_, kb = (b.shape[1], b.shape[0]) if b_mn else b.shape
+        assert k == kb, f"K mismatch {k} vs {kb}"
+        if out is None:
+            assert not accumulate
+            out = torch.empty(m, nn_, dtype=a.dtype, device=a.device)
+        A[i], B[i], C[i] = a.data_ptr(), b.data_ptr(), out.data_ptr()
+        M[i], N[i], K[i] = m, nn_, k
+        lda[i], ldb[i], ldc[i] = a.stride(0), b.stride(0), out.stride(0)
+        amn[i], bmn[i], acc[i] = int(a_mn), int(b_mn), int(accumulate)
+        outs.append(out)
+    native.call("lb_gemm_grouped", n, A, B, C, M, N, K, lda, ldb, ldc, amn, bmn, acc, native.stream_ptr())
+    return outs
+
+
+_GROUP_BWD = os.environ.get("LIGHTRON_GROUPED_BWD", "1") != "0"
 
 
 class _Linear(torch.autograd.Function):
@@ -81,6 +114,16 @@ class _Linear(torch.autograd.Function):
             dy2 = dy2.contiguous()
         sizes = [w.shape[0] for w in ws]
         dx = None
+        if _GROUP_BWD and ctx.fused and ctx.needs_input_grad[0] and any(ctx.needs_input_grad[1:]):
+            # data gradient and weight gradient in one launch: the short dgrad tiles fill the
+            # last, partly empty wave of the wgrad
+            dx, dw = gemm_grouped([(dy2, x2, True, True, None, False),
+                                   (dy2, _as_strided_cat(ws), False, True, None, False)])[::-1]
+            dws, off = [], 0
+            for n in sizes:
+                dws.append(dw[off:off + n])
+                off += n
+            return (dx.view(ctx.xshape), *dws)
         if ctx.needs_input_grad[0]:
             if ctx.fused:
                 dx = gemm(dy2, _as_strided_cat(ws), b_mn=True)

@@ -21,7 +21,9 @@ def _gemm_status():
     from lightron_b200.ops import native
     buf = (ctypes.c_uint * 4)()
     native.require().lb_device_status(ctypes.cast(buf, ctypes.c_void_p))
-    return list(buf)
+    buf2 = (ctypes.c_uint * 4)()
+    native.require().lb_gemm_grouped_status(ctypes.cast(buf2, ctypes.c_void_p))
+    return [a | b for a, b in zip(buf, buf2)]
 
 
 def _rel_err(got, want):
@@ -34,7 +36,8 @@ def _rel_err(got, want):
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)],
                          ids=["kk", "kmn", "mnmn", "mnk"])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 264, 200), (1000, 1032, 520), (4096, 2560, 2048)])
-def test_gemm_all_majors(M, N, K, a_mn, b_mn):
+@pytest.mark.parametrize("legacy", [False, True], ids=["grouped1", "plain"])
+def test_gemm_all_majors(M, N, K, a_mn, b_mn, legacy):
     from lightron_b200.ops import functional as OF
     if a_mn and M % 8:
         pytest.skip("MN-major A needs M % 8 == 0")
@@ -43,12 +46,57 @@ def test_gemm_all_majors(M, N, K, a_mn, b_mn):
     want = a.float() @ b.float().t()
     a_arg = a.t().contiguous() if a_mn else a
     b_arg = b.t().contiguous() if b_mn else b
-    got = OF.gemm(a_arg, b_arg, a_mn=a_mn, b_mn=b_mn)
+    got = OF.gemm(a_arg, b_arg, a_mn=a_mn, b_mn=b_mn, legacy=legacy)
     torch.cuda.synchronize()
     st = _gemm_status()
     assert st[0] == 0, f"device status {st}"
     err = _rel_err(got, want)
     assert err < 5e-3, f"rel err {err} (a_mn={a_mn}, b_mn={b_mn}, {M}x{N}x{K}); max abs {(got.float()-want).abs().max().item()}"
+
+
+def test_gemm_grouped_mixed_problems():
+    """Four problems of different size and operand majors in one launch, one of them accumulating
+    into its output; every result against fp32 matmul."""
+    import ctypes
+    from lightron_b200.ops import functional as OF, native
+    specs = [(2048, 1536, 512, False, True), (520, 264, 4096, True, True), (128, 256, 64, False, False),
+             (1000, 1032, 520, True, False)]
+    probs, wants = [], []
+    for i, (M, N, K, a_mn, b_mn) in enumerate(specs):
+        a, b = _rand(M, K, seed=10 + i), _rand(N, K, seed=20 + i)
+        want = a.float() @ b.float().t()
+        out, acc = None, False
+        if i == 1:
+            out, acc = _rand(M, N, seed=30), True
+            want = want + out.float()
+        probs.append((a.t().contiguous() if a_mn else a, b.t().contiguous() if b_mn else b, a_mn, b_mn, out, acc))
+        wants.append(want)
+    for _ in range(2):                                   # second call reuses the cached schedule
+        if probs[1][4] is not None:
+            probs[1] = probs[1][:4] + (_rand(520, 264, seed=30), True)
+        outs = OF.gemm_grouped(probs)
+        torch.cuda.synchronize()
+        buf = (ctypes.c_uint * 4)()
+        native.require().lb_gemm_grouped_status(ctypes.cast(buf, ctypes.c_void_p))
+        assert buf[0] == 0, f"device status {list(buf)}"
+        for got, want in zip(outs, wants):
+            assert _rel_err(got, want) < 5e-3
+
+
+def test_linear_backward_grouped_matches_separate(monkeypatch):
+    from lightron_b200.ops import functional as OF
+    x = _rand(1024, 512, seed=1).requires_grad_(True)
+    w = _rand(776, 512, seed=2, scale=0.05).requires_grad_(True)
+    dy = _rand(1024, 776, seed=3)
+    grads = []
+    for flag in (True, False):
+        monkeypatch.setattr(OF, "_GROUP_BWD", flag)
+        x.grad = w.grad = None
+        OF.linear(x, w).backward(dy)
+        grads.append((x.grad.clone(), w.grad.clone()))
+    assert _rel_err(grads[0][0], grads[1][0]) < 1e-3 and _rel_err(grads[0][1], grads[1][1]) < 1e-3
+    assert _rel_err(grads[0][0], dy.float() @ w.detach().float()) < 5e-3
+    assert _rel_err(grads[0][1], dy.float().t() @ x.detach().float()) < 5e-3
 
 
 def test_gemm_strided_operands_and_output():
