@@ -89,6 +89,7 @@ def gemm_grouped(problems) -> List[torch.Tensor]:
 
 
 _GROUP_BWD = os.environ.get("LIGHTRON_GROUPED_BWD", "1") != "0"
+_DIRECT_WGRAD = os.environ.get("LIGHTRON_DIRECT_WGRAD", "1") != "0"
 
 
 class _Linear(torch.autograd.Function):
@@ -99,6 +100,7 @@ class _Linear(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         ctx.fused = _rows_adjacent(ws)
         ctx.save_for_backward(x2, *ws)
+        ctx.params = ws
         ctx.xshape = x.shape
         if ctx.fused:
             y = gemm(x2, _as_strided_cat(ws))
@@ -117,6 +119,18 @@ class _Linear(torch.autograd.Function):
         if _GROUP_BWD and ctx.fused and ctx.needs_input_grad[0] and any(ctx.needs_input_grad[1:]):
             # data gradient and weight gradient in one launch: the short dgrad tiles fill the
             # last, partly empty wave of the wgrad
+            params = ctx.params
+            if _DIRECT_WGRAD and all(getattr(w, "_lb_direct_grad", False) and w.grad is not None for w in params) \
+                    and all(ctx.needs_input_grad[1:]) and _rows_adjacent([w.grad for w in params]):
+                # the weight gradient accumulates straight into the gradient arena in the GEMM
+                # epilogue: no separate add, and the optimizer's bucket hooks are called by hand
+                gout = _as_strided_cat([w.grad for w in params])
+                dx = gemm_grouped([(dy2, x2, True, True, gout, True),
+                                   (dy2, _as_strided_cat(ws), False, True, None, False)])[1]
+                for w in params:
+                    for hook in getattr(w, "_lb_grad_hooks", ()):
+                        hook(w)
+                return (dx.view(ctx.xshape), *([None] * len(ws)))
             dx, dw = gemm_grouped([(dy2, x2, True, True, None, False),
                                    (dy2, _as_strided_cat(ws), False, True, None, False)])[::-1]
             dws, off = [], 0

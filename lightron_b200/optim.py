@@ -35,7 +35,7 @@ _ALIGN = 128
 
 
 class _Bucket:
-    __slots__ = ("start", "end", "group", "n", "shard_len", "shard_off", "pending", "n_params", "launched", "event")
+    __slots__ = ("start", "end", "group", "n", "shard_len", "shard_off", "pending", "n_params", "launched", "event", "seen")
 
     def __init__(self, start, end, group, n, shard_off):
         self.start, self.end, self.group, self.n = start, end, group, n
@@ -44,6 +44,7 @@ class _Bucket:
         self.pending = self.n_params = 0
         self.launched = False
         self.event = None
+        self.seen = set()
 
 
 def arrange_parameters(model: nn.Module) -> List[nn.Parameter]:
@@ -163,7 +164,12 @@ class DistributedAdamW:
                 if off < b.end and off + p.numel() > b.start:
                     b.n_params += 1
                     if self.overlap and p.requires_grad:
-                        p.register_post_accumulate_grad_hook(self._make_hook(b))
+                        hook = self._make_hook(b)
+                        p.register_post_accumulate_grad_hook(hook)
+                        # ops that write a gradient straight into the arena (no autograd
+                        # accumulation, hence no post-accumulate callback) call these themselves
+                        p._lb_grad_hooks = getattr(p, "_lb_grad_hooks", ()) + (hook,)
+            p._lb_direct_grad = bool(flat.is_cuda and flat.dtype == torch.bfloat16 and native.available())
         self._reset_buckets()
         # parameters whose gradient is a partial sum over the TP group (norm weights under
         # sequence parallelism: every TP rank saw only its own rows)
@@ -195,12 +201,19 @@ class DistributedAdamW:
     # ---- gradient synchronisation ---------------------------------------------------------
     def _reset_buckets(self):
         for b in self.buckets:
-            b.pending, b.launched, b.event = b.n_params, False, None
+            b.pending, b.launched, b.event, b.seen = b.n_params, False, None, set()
 
     def _make_hook(self, b: _Bucket):
-        def hook(_p):
+        def hook(p):
+            # Counts every parameter once per synchronised backward pass.  An op that wrote the
+            # gradient straight into the arena calls this by hand, and autograd may call it again
+            # for the same parameter (it runs the post-accumulate callbacks even when the op
+            # returned no gradient), hence the set.  Micro-batches without sync do not count.
+            if not self.sync_enabled or id(p) in b.seen:
+                return
+            b.seen.add(id(p))
             b.pending -= 1
-            if b.pending == 0 and self.sync_enabled and not self.sp_partial:
+            if b.pending == 0 and not self.sp_partial:
                 self._launch_reduce(b, async_op=True)
         return hook
 
