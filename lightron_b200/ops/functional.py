@@ -88,6 +88,56 @@ def gemm_grouped(problems) -> List[torch.Tensor]:
     return outs
 
 
+# ---- deferred weight gradients ------------------------------------------------------------------
+# A lone weight-gradient GEMM often fills the 148 SMs badly (a [1280, 2048] gradient is 80 tiles).
+# Ops whose parameters' gradients live in the optimizer's arena may queue the product instead of
+# launching it; the queue is flushed as ONE grouped launch (tiles of several gradients share the
+# waves) at the latest when the backward pass ends, and the optimizer's bucket callbacks run then.
+
+_WQ: List[tuple] = []
+_WQ_STATE = {"callback": False}
+_DEFER_WGRAD = os.environ.get("LIGHTRON_DEFER_WGRAD", "1") != "0"
+
+
+def direct_wgrad_ok(params) -> bool:
+    """True when every weight's ``.grad`` is a row-adjacent view of the bf16 gradient arena."""
+    return bool(params) and all(getattr(w, "_lb_direct_grad", False) and w.grad is not None for w in params) \
+        and _rows_adjacent([w.grad for w in params])
+
+
+def wgrad_queue_uses(tag) -> bool:
+    return any(t == tag for *_rest, t in _WQ)
+
+
+def defer_wgrad(dy2: torch.Tensor, x2: torch.Tensor, params, tag=None) -> None:
+    """Queue  grad(params) += dy2^T x2  (dy2 [tokens, sum n_i], x2 [tokens, K]).  ``tag`` lets the
+    caller ask later whether an entry with that tag is still pending (buffers that get recycled)."""
+    for w in params:
+        w._lb_wgrad_pending = True
+    _WQ.append((dy2, x2, tuple(params), tag))
+    if not _WQ_STATE["callback"]:
+        _WQ_STATE["callback"] = True
+        torch.autograd.Variable._execution_engine.queue_callback(flush_wgrads)
+    if len(_WQ) >= 8:
+        flush_wgrads(final=False)
+
+
+def flush_wgrads(final: bool = True) -> None:
+    if final:
+        _WQ_STATE["callback"] = False
+    if not _WQ:
+        return
+    items = list(_WQ)
+    _WQ.clear()
+    gemm_grouped([(dy2, x2, True, True, _as_strided_cat([w.grad for w in params]), True)
+                  for dy2, x2, params, _tag in items])
+    for _dy2, _x2, params, _tag in items:
+        for w in params:
+            w._lb_wgrad_pending = False
+            for hook in getattr(w, "_lb_grad_hooks", ()):
+                hook(w)
+
+
 _GROUP_BWD = os.environ.get("LIGHTRON_GROUPED_BWD", "1") != "0"
 _DIRECT_WGRAD = os.environ.get("LIGHTRON_DIRECT_WGRAD", "1") != "0"
 
@@ -120,8 +170,7 @@ class _Linear(torch.autograd.Function):
             # data gradient and weight gradient in one launch: the short dgrad tiles fill the
             # last, partly empty wave of the wgrad
             params = ctx.params
-            if _DIRECT_WGRAD and all(getattr(w, "_lb_direct_grad", False) and w.grad is not None for w in params) \
-                    and all(ctx.needs_input_grad[1:]) and _rows_adjacent([w.grad for w in params]):
+            if _DIRECT_WGRAD and all(ctx.needs_input_grad[1:]) and direct_wgrad_ok(params):
                 # the weight gradient accumulates straight into the gradient arena in the GEMM
                 # epilogue: no separate add, and the optimizer's bucket hooks are called by hand
                 gout = _as_strided_cat([w.grad for w in params])

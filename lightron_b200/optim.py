@@ -28,7 +28,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from . import mesh as _mesh
-from .ops import native, reference as ref
+from .ops import functional as OF, native, reference as ref
 from .parallel import comm
 
 _ALIGN = 128
@@ -209,8 +209,8 @@ class DistributedAdamW:
             # gradient straight into the arena calls this by hand, and autograd may call it again
             # for the same parameter (it runs the post-accumulate callbacks even when the op
             # returned no gradient), hence the set.  Micro-batches without sync do not count.
-            if not self.sync_enabled or id(p) in b.seen:
-                return
+            if not self.sync_enabled or id(p) in b.seen or getattr(p, "_lb_wgrad_pending", False):
+                return                      # (a queued weight gradient calls back when it has been launched)
             b.seen.add(id(p))
             b.pending -= 1
             if b.pending == 0 and not self.sp_partial:
@@ -258,6 +258,7 @@ class DistributedAdamW:
         self.sync_enabled = bool(flag)
 
     def finish_grad_sync(self):
+        OF.flush_wgrads()                   # normally empty: the queue is flushed when backward ends
         if self.sp_partial:
             buf = torch.cat([p.grad.reshape(-1).float() for p in self.sp_partial])
             dist.all_reduce(buf, group=self.ctx.tp_group)

@@ -213,6 +213,9 @@ def gemm_rs(x: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False) -> torc
 # ---- autograd -------------------------------------------------------------------------------------------
 
 
+_SCRATCH_TAG = "symm-scratch-gather"
+
+
 class AllGatherLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_local, group, *ws):
@@ -224,6 +227,7 @@ class AllGatherLinear(torch.autograd.Function):
             y0, gathered, tag = ag_gemm(x_local, ws[0], group, keep=True)
             y = torch.cat([y0] + [OF.gemm(gathered, w) for w in ws[1:]], dim=1)
         ctx.save_for_backward(*ws)
+        ctx.params = ws
         ctx.gathered, ctx.tag = gathered, tag
         ctx.group, ctx.fused = group, fused
         return y
@@ -248,6 +252,11 @@ class AllGatherLinear(torch.autograd.Function):
                 off += nn_
             from . import comm
             dx = comm.reduce_scatter_rows(full, ctx.group)
+        if OF._DEFER_WGRAD and ctx.fused and all(ctx.needs_input_grad[2:]) and OF.direct_wgrad_ok(ctx.params):
+            # queued: launched together with the neighbouring layers' weight gradients.  The gathered
+            # activation sits in the keep ring, which nobody overwrites before the next forward.
+            OF.defer_wgrad(dy, gathered, ctx.params)
+            return (dx, None, *([None] * len(ws)))
         dw = OF.gemm(dy, gathered, a_mn=True, b_mn=True)
         dws, off = [], 0
         for nn_ in sizes:
@@ -261,12 +270,20 @@ class LinearReduceScatter(torch.autograd.Function):
     def forward(ctx, x, w, group):
         x = x.contiguous()
         ctx.save_for_backward(x, w)
+        ctx.params = (w,)
         ctx.group = group
         return gemm_rs(x, w, group)
 
     @staticmethod
     def backward(ctx, dy_local):
         x, w = ctx.saved_tensors
+        # A queued weight gradient that reads a scratch gather buffer must be launched before this
+        # rank's next scratch gather: until then no peer can have reached the call that recycles it.
+        if OF.wgrad_queue_uses(_SCRATCH_TAG):
+            OF.flush_wgrads(final=False)
         dx, dy_full, _ = ag_gemm(dy_local.contiguous(), w, ctx.group, b_mn=True, keep=False)
+        if OF._DEFER_WGRAD and ctx.needs_input_grad[1] and OF.direct_wgrad_ok(ctx.params):
+            OF.defer_wgrad(dy_full, x, ctx.params, tag=_SCRATCH_TAG)
+            return dx, None, None
         dw = OF.gemm(dy_full, x, a_mn=True, b_mn=True)
         return dx, dw, None
