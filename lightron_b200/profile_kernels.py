@@ -1,6 +1,6 @@
 """Small, self-terminating workloads for profiling single kernels under ncu.
 
-    python -m lightron_b200.profile_kernels gemm|attn|norm
+    python -m lightron_b200.profile_kernels gemm|grouped|normbwd|attn|norm
 
 Each mode launches its kernel a few times on inputs larger than L2 but well under 1 GB, prints
 CUDA-event timings and exits; capture with e.g.
@@ -54,8 +54,34 @@ def main(mode: str) -> None:
         ms = _time(lambda: OF.add_rmsnorm(x, r, w, 1e-5))
         gb = 4 * rows * cols * 2 / 1e9
         print(f"add_rmsnorm fwd {rows}x{cols}: {ms:.3f} ms  {gb / ms * 1e3:.0f} GB/s")
+    elif mode == "grouped":
+        # data gradient of the 1.1B model's gate+up projection: plain kernel, grouped kernel with
+        # that one problem, then the layer's data + weight gradient as one grouped launch
+        T, N, K = 16384, 11264, 2048
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+        x = torch.randn(T, K, device=dev, dtype=torch.bfloat16)
+        dy = torch.randn(T, N, device=dev, dtype=torch.bfloat16)
+        fl = 2.0 * T * N * K
+        t_plain = _time(lambda: OF.gemm(dy, w, b_mn=True, legacy=True), iters=3)
+        t_one = _time(lambda: OF.gemm_grouped([(dy, w, False, True, None, False)]), iters=3)
+        t_w = _time(lambda: OF.gemm(dy, x, a_mn=True, b_mn=True, legacy=True), iters=3)
+        t_pair = _time(lambda: OF.gemm_grouped([(dy, x, True, True, None, False), (dy, w, False, True, None, False)]),
+                       iters=3)
+        print(f"dgrad {T}x{K}x{N}: plain {t_plain:.3f} ms ({fl / t_plain / 1e9:.0f} TFLOP/s), grouped(1) {t_one:.3f} ms "
+              f"({fl / t_one / 1e9:.0f}); plain wgrad {t_w:.3f} ms; dgrad+wgrad grouped {t_pair:.3f} ms "
+              f"({2 * fl / t_pair / 1e9:.0f} TFLOP/s) vs {t_plain + t_w:.3f} ms separate")
+    elif mode == "normbwd":
+        rows, cols = 32768, 2048                       # 128 MiB per tensor
+        x = torch.randn(rows, cols, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        r = torch.randn(rows, cols, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        w = torch.ones(cols, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        h, y = OF.add_rmsnorm(x, r, w, 1e-5)
+        dh, dyy = torch.randn_like(h), torch.randn_like(y)
+        ms = _time(lambda: torch.autograd.grad([h, y], [x, r, w], [dh, dyy], retain_graph=True), iters=3)
+        gb = 4 * rows * cols * 2 / 1e9                 # dy, x, dres in; dx out (dx doubles as the residual gradient)
+        print(f"add_rmsnorm bwd {rows}x{cols}: {ms:.3f} ms  {gb / ms * 1e3:.0f} GB/s (autograd call, both kernels)")
     else:
-        raise SystemExit("mode: gemm | attn | norm")
+        raise SystemExit("mode: gemm | grouped | normbwd | attn | norm")
 
 
 if __name__ == "__main__":
