@@ -38,7 +38,6 @@ struct FaBwdParams {
   long long o_ts, do_ts, dq_ts, dk_ts, dv_ts;
   float scale;
   int causal;
-  int debug;
   int kv_brows;   // rows between consecutive batches in the K/V tensor maps (>= Sk)
 };
 
@@ -503,7 +502,7 @@ static int flash_bwd_tc_impl(int kv_brows, const void* q, const void* k, const v
     return LB_ERR_ARG;
   FaBwdParams p{(const bf16*)o, (const bf16*)dout, (const float*)lse, (float*)delta, (float*)dq_acc,
                 (bf16*)dq, (bf16*)dk, (bf16*)dv, B, Sq, Sk, hq, hkv, o_ts, do_ts, dq_ts, dk_ts, dv_ts, scale, causal,
-                0, kv_brows};
+                kv_brows};
   cudaStream_t s = (cudaStream_t)stream;
   switch (d) {
     case 64: return launch_fa_bwd<64>(q, k, v, p, q_ts, k_ts, v_ts, s);

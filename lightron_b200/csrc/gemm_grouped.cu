@@ -291,17 +291,25 @@ int g_sms = 0;
 
 // Longest tiles first, each to the least loaded CTA (ties: lowest CTA index, which keeps tiles
 // that run at the same time adjacent in the problem's L2-friendly order).
-int build_schedule(const Problem* probs, int np, int sms, Schedule* out) {
-  struct Item { int cost, code; };
+struct Item { int cost, code; };
+
+// The assignment itself (host only): per-CTA item lists, longest tiles first, each to the least
+// loaded CTA.  Returns the load (in k-block units) of the busiest CTA.
+long long assign_items(const Problem* probs, int np, int sms, std::vector<std::vector<int>>* per_out, int* total_out,
+                       long long* work_out) {
   std::vector<Item> items;
   std::vector<int> order(np);
   for (int i = 0; i < np; i++) order[i] = i;
   std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return probs[a].num_kb > probs[b].num_kb; });
+  long long work = 0;
   for (int oi = 0; oi < np; oi++) {
     const int i = order[oi];
     const int nt = probs[i].tiles_m * probs[i].tiles_n;
-    if (nt >= (1 << 24)) return LB_ERR_SHAPE;
-    for (int t = 0; t < nt; t++) items.push_back({probs[i].num_kb + 6, (i << 24) | t});   // +6: fixed cost per tile
+    if (nt >= (1 << 24)) return -1;
+    for (int t = 0; t < nt; t++) {
+      items.push_back({probs[i].num_kb + 6, (i << 24) | t});   // +6: fixed cost per tile
+      work += probs[i].num_kb + 6;
+    }
   }
   const int total = (int)items.size();
   const int grid = total < sms ? total : sms;
@@ -309,12 +317,26 @@ int build_schedule(const Problem* probs, int np, int sms, Schedule* out) {
   std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
   for (int c = 0; c < grid; c++) heap.push({0, c});
   std::vector<std::vector<int>> per(grid);
+  long long busiest = 0;
   for (const Item& it : items) {
     Load l = heap.top();
     heap.pop();
     per[l.second].push_back(it.code);
-    heap.push({l.first + it.cost, l.second});
+    const long long load = l.first + it.cost;
+    if (load > busiest) busiest = load;
+    heap.push({load, l.second});
   }
+  if (per_out) per_out->swap(per);
+  if (total_out) *total_out = total;
+  if (work_out) *work_out = work;
+  return busiest;
+}
+
+int build_schedule(const Problem* probs, int np, int sms, Schedule* out) {
+  std::vector<std::vector<int>> per;
+  int total = 0;
+  if (assign_items(probs, np, sms, &per, &total, nullptr) < 0) return LB_ERR_SHAPE;
+  const int grid = (int)per.size();
   std::vector<int> offsets(grid + 1, 0), flat;
   flat.reserve(total);
   for (int c = 0; c < grid; c++) {
@@ -338,6 +360,25 @@ extern "C" int lb_gemm_grouped_status(void* out) {
   if (e != cudaSuccess) { g_lb_last_cuda_error = (int)e; return LB_ERR_LAUNCH; }
   unsigned int zeros[4] = {0, 0, 0, 0};
   cudaMemcpyToSymbol(g_grp_status, zeros, sizeof(zeros));
+  return LB_OK;
+}
+
+// Host only (no CUDA call): the schedule lb_gemm_grouped would build for these shapes on `sms` SMs.
+// out[0] = load of the busiest CTA, out[1] = total work, out[2] = number of CTAs used, all in k-block
+// units of 64 (a tile counts its k-blocks + 6).  busiest * CTAs / total is the imbalance factor.
+extern "C" int lb_gemm_grouped_plan(int n, const int* M, const int* N, const int* K, int sms, long long* out) {
+  if (n < 1 || n > MAX_PROBLEMS || sms < 1) return LB_ERR_SHAPE;
+  Problem probs[MAX_PROBLEMS];
+  for (int i = 0; i < n; i++) {
+    if (M[i] <= 0 || N[i] <= 0 || K[i] <= 0) return LB_ERR_SHAPE;
+    probs[i].tiles_m = (M[i] + BM - 1) / BM; probs[i].tiles_n = (N[i] + BN - 1) / BN; probs[i].num_kb = (K[i] + BK - 1) / BK;
+  }
+  std::vector<std::vector<int>> per;
+  int total = 0;
+  long long work = 0;
+  const long long busiest = assign_items(probs, n, sms, &per, &total, &work);
+  if (busiest < 0) return LB_ERR_SHAPE;
+  out[0] = busiest; out[1] = work; out[2] = (long long)per.size();
   return LB_OK;
 }
 

@@ -36,6 +36,25 @@ class MoEFeedForward(nn.Module):
         self.tp_group = ctx.tp_group if args.tp_size > 1 else None
         self.last_aux_loss = None
 
+    def _apply_experts(self, tokens: torch.Tensor, meta) -> torch.Tensor:
+        """Local expert e on its contiguous segment of ``tokens``: one grouped GEMM launch for the
+        gate+up projections of all local experts, SwiGLU, one for the down projections (K14 of the
+        kernel list: the reference runs a single expert, model/model.py:109).  With tensor-parallel
+        experts, or before the parameters sit in the flat arena, experts run one after the other."""
+        mlps = list(self.experts.values())
+        up = [(m.w1.weight, m.w3.weight) for m in mlps]
+        down = [(m.w2.weight,) for m in mlps]
+        if self.tp_group is None and tokens.shape[0] > 0 and OF.grouped_linear_ok(tokens, up) \
+                and OF.grouped_linear_ok(tokens, down):
+            counts = meta.expert_counts
+            if self.ep.ep_size == 1:
+                counts = counts[self.ep.first_expert:self.ep.first_expert + self.ep.local_experts]
+            counts = [int(c) for c in counts]
+            gu = OF.grouped_linear(tokens, counts, up)
+            return OF.grouped_linear(OF.swiglu(gu), counts, down)
+        experts = [lambda t, m=m: m(t, sp=False) for m in mlps]
+        return self.ep.apply_experts(tokens, meta, experts)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """x [T, H] -> [T, H]."""
         from ..parallel import comm
@@ -50,8 +69,7 @@ class MoEFeedForward(nn.Module):
             frac = torch.bincount(indices.reshape(-1), minlength=self.num_experts).float() / (T * self.topk)
         self.last_aux_loss = self.num_experts * torch.sum(frac * probs.mean(dim=0))
         tokens, meta = self.ep.dispatch(x, indices)
-        experts = [lambda t, m=m: m(t, sp=False) for m in self.experts.values()]
-        y = self.ep.apply_experts(tokens, meta, experts)
+        y = self._apply_experts(tokens, meta)
         y = self.ep.combine(y, meta)                             # [T, k, H]
         out = (y.float() * weights.unsqueeze(-1)).sum(dim=1).to(x.dtype)
         if self.sp:

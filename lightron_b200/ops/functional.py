@@ -207,6 +207,93 @@ class _Linear(torch.autograd.Function):
         return (dx, *dws)
 
 
+def _grouped_launch(problems) -> None:
+    for i in range(0, len(problems), 8):
+        gemm_grouped(problems[i:i + 8])
+
+
+class _GroupedLinear(torch.autograd.Function):
+    """Row segments of ``x`` times different weights: segment e (``counts[e]`` rows) uses the
+    row-adjacent weights ``groups[e]``.  All segments run in one grouped launch (forward: one
+    problem per segment; backward: data and weight gradient of every segment together)."""
+
+    @staticmethod
+    def forward(ctx, x, counts, per_group, *flat_ws):
+        groups = [flat_ws[i:i + per_group] for i in range(0, len(flat_ws), per_group)]
+        N = sum(w.shape[0] for w in groups[0])
+        y = torch.empty(x.shape[0], N, dtype=x.dtype, device=x.device)
+        probs, off = [], 0
+        for c, ws in zip(counts, groups):
+            if c:
+                probs.append((x[off:off + c], _as_strided_cat(ws), False, False, y[off:off + c], False))
+            off += c
+        if off < x.shape[0]:
+            y[off:].zero_()
+        _grouped_launch(probs)
+        ctx.save_for_backward(x, *flat_ws)
+        ctx.counts, ctx.per_group, ctx.params = list(counts), per_group, flat_ws
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, *flat_ws = ctx.saved_tensors
+        per = ctx.per_group
+        groups = [flat_ws[i:i + per] for i in range(0, len(flat_ws), per)]
+        pgroups = [ctx.params[i:i + per] for i in range(0, len(flat_ws), per)]
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        direct = _DIRECT_WGRAD and all(ctx.needs_input_grad[3:]) and all(direct_wgrad_ok(pg) for pg in pgroups)
+        probs, dws, off = [], [], 0
+        for c, ws, pg in zip(ctx.counts, groups, pgroups):
+            if direct:
+                gout, acc = (_as_strided_cat([w.grad for w in pg]), True)
+            else:
+                gout, acc = (torch.zeros(sum(w.shape[0] for w in ws), x.shape[1], dtype=x.dtype, device=x.device), False)
+                dws.append(gout)
+            if c:
+                probs.append((dy[off:off + c], x[off:off + c], True, True, gout, acc))           # wgrad first: longest tiles
+                probs.append((dy[off:off + c], _as_strided_cat(ws), False, True, dx[off:off + c], False))
+            off += c
+        if off < x.shape[0]:
+            dx[off:].zero_()
+        _grouped_launch(probs)
+        if direct:
+            for pg in pgroups:
+                for w in pg:
+                    for hook in getattr(w, "_lb_grad_hooks", ()):
+                        hook(w)
+            return (dx, None, None, *([None] * len(flat_ws)))
+        out = []
+        for dw, ws in zip(dws, groups):
+            o = 0
+            for w in ws:
+                out.append(dw[o:o + w.shape[0]])
+                o += w.shape[0]
+        return (dx, None, None, *out)
+
+
+def grouped_linear_ok(x: torch.Tensor, groups) -> bool:
+    return bool(native.use_native(x) and x.shape[-1] % 8 == 0 and groups
+                and all(_rows_adjacent(ws) and all(w.shape[0] % 8 == 0 for w in ws) for ws in groups))
+
+
+def grouped_linear(x: torch.Tensor, counts, groups) -> torch.Tensor:
+    """x [R, K], rows sorted by segment; segment e has ``counts[e]`` rows and is multiplied by the
+    weights ``groups[e]`` (a tuple of [n_i, K] matrices whose outputs are concatenated, as in
+    :func:`linear`).  Rows beyond ``sum(counts)`` give zeros.  The per-expert GEMM of a MoE layer
+    (one launch for all local experts; the reference applies a single expert, model/model.py:109)."""
+    if grouped_linear_ok(x, groups):
+        flat = [w for ws in groups for w in ws]
+        return _GroupedLinear.apply(x, list(counts), len(groups[0]), *flat)
+    outs, off = [], 0
+    for c, ws in zip(counts, groups):
+        outs.append(linear(x[off:off + c], *ws))
+        off += c
+    if off < x.shape[0]:
+        outs.append(x.new_zeros(x.shape[0] - off, outs[0].shape[1]))
+    return torch.cat(outs, dim=0)
+
+
 def linear(x: torch.Tensor, *ws: torch.Tensor) -> torch.Tensor:
     """x [..., K] times one or more [n_i, K] weights -> [..., sum n_i]."""
     if native.use_native(x) and x.shape[-1] % 8 == 0 and all(w.shape[0] % 8 == 0 for w in ws):

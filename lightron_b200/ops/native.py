@@ -45,6 +45,7 @@ _SIGNATURES = {
     "lb_gemm_bf16": [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _I, _P],
     "lb_gemm_grouped": [_I] + [_P] * 13,
     "lb_gemm_grouped_status": [_P],
+    "lb_gemm_grouped_plan": [_I, _P, _P, _P, _I, _P],
     "lb_gemm_ag": [_P, _P, _I, _I, _I, _L, _L, _I, _I, _I, _P, _L, _P, _P, ctypes.c_uint, _I, _P],
     "lb_gemm_rs": [_P, _P, _I, _I, _I, _L, _L, _I, _I, _I, _P, _P, ctypes.c_uint, _P, _L, _P],
     "lb_dp_status": [_P],
