@@ -346,16 +346,6 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       if (m_i != -INFINITY && (m_new - m_i) * sl2 <= 8.f) m_new = m_i;
       const float m_s = (m_new == -INFINITY) ? 0.f : m_new * sl2;
       const float corr = (m_i == -INFINITY) ? 0.f : exp2f(m_i * sl2 - m_s);
-      float rs = 0.f;
-      uint32_t pb[64];
-#pragma unroll
-      for (int i = 0; i < 128; i += 2) {
-        const float e0 = exp2f(fmaf(__uint_as_float(r[i]), sl2, -m_s));
-        const float e1 = exp2f(fmaf(__uint_as_float(r[i + 1]), sl2, -m_s));
-        rs += e0 + e1;
-        bf162 pk = __floats2bfloat162_rn(e0, e1);
-        pb[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
-      }
       if (j > 0) {
         // previous P V finished: O is stable and the P buffer may be overwritten
         if (!mbar_wait(pv_done(t), (uint32_t)(j - 1) & 1u, abort_flag)) { ok = false; break; }
@@ -373,10 +363,24 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
           tmem_st_wait();
         }
       }
+      // exponentials, 8 columns at a time, packed and stored to the P tile at once: the row of
+      // scores is the only large array that stays in registers (no spills)
+      float rs = 0.f;
 #pragma unroll
-      for (int cc = 0; cc < 16; cc++)
+      for (int cc = 0; cc < 16; cc++) {
+        uint32_t pk4[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const int i = cc * 8 + q * 2;
+          const float e0 = exp2f(fmaf(__uint_as_float(r[i]), sl2, -m_s));
+          const float e1 = exp2f(fmaf(__uint_as_float(r[i + 1]), sl2, -m_s));
+          rs += e0 + e1;
+          bf162 pk = __floats2bfloat162_rn(e0, e1);
+          pk4[q] = *reinterpret_cast<uint32_t*>(&pk);
+        }
         *reinterpret_cast<uint4*>(sP + (cc >> 3) * C::ATOM_BYTES + sw128_off(rit, cc & 7)) =
-            make_uint4(pb[cc * 4], pb[cc * 4 + 1], pb[cc * 4 + 2], pb[cc * 4 + 3]);
+            make_uint4(pk4[0], pk4[1], pk4[2], pk4[3]);
+      }
       l_i = l_i * corr + rs;
       m_i = m_new;
       fence_before();
