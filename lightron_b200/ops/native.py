@@ -139,3 +139,29 @@ def call(name: str, *args) -> None:
     _LAUNCHES += 1
     if rc != 0:
         raise NativeError(f"{name} failed: {_ERRORS.get(rc, rc)} (cuda error {lib.lb_last_error()})")
+
+
+_STATUS_READERS = (("lb_device_status", "GEMM / fused collective GEMM"), ("lb_gemm_grouped_status", "grouped GEMM"),
+                   ("lb_flash_status", "attention forward"), ("lb_flash_bwd_status", "attention backward"),
+                   ("lb_dp_status", "data-parallel optimizer kernel"))
+
+
+def device_status() -> dict:
+    """Status words of every kernel family that has bounded waits: ``{family: (code, where)}`` for the
+    families whose wait ran out since the last read (reading clears them; synchronises the device)."""
+    lib = require()
+    out = {}
+    buf = (ctypes.c_uint * 4)()
+    for sym, family in _STATUS_READERS:
+        getattr(lib, sym)(ctypes.cast(buf, ctypes.c_void_p))
+        if buf[0]:
+            out[family] = (int(buf[0]), int(buf[1]))
+    return out
+
+
+def raise_on_device_status() -> None:
+    """Turn a bounded wait that ran out inside a kernel (a peer that never arrived, a lost barrier)
+    into a Python error at the next host synchronisation point instead of silently wrong numbers."""
+    bad = device_status()
+    if bad:
+        raise RuntimeError("device-side wait ran out: " + ", ".join(f"{k} (code {c}, where {w})" for k, (c, w) in bad.items()))

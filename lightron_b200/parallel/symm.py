@@ -158,6 +158,9 @@ def check_status() -> None:
     native.require().lb_device_status(ctypes.cast(buf, ctypes.c_void_p))
     if buf[0]:
         raise RuntimeError(f"fused comm kernel gave up waiting (code {buf[0]}, where {buf[1]}): a peer did not arrive")
+    native.require().lb_gemm_grouped_status(ctypes.cast(buf, ctypes.c_void_p))
+    if buf[0]:
+        raise RuntimeError(f"grouped GEMM kernel gave up waiting (code {buf[0]}, where {buf[1]})")
 
 
 # ---- raw ops ------------------------------------------------------------------------------------------

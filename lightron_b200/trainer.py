@@ -23,6 +23,7 @@ from . import mesh as _mesh
 from .config import RunConfig, build_model_args, load_config
 from .data import MicroBatchDataLoader
 from .models.llama import LightronTransformer, init_weights
+from .ops import native
 from .optim import DistributedAdamW
 from .parallel import fused
 from .parallel.pp import PipelineParallel, init_pp_group_manager, train_step_pipeline_1f1b, train_step_pipeline_afab
@@ -162,6 +163,8 @@ class Trainer:
                     dist.all_reduce(loss, group=ctx.dpcp_group)
                     loss = loss / ctx.grad_replicas
                 last_loss = float(loss)                            # the only host sync, once per log interval
+                if self.device.type == "cuda" and native.available():
+                    native.raise_on_device_status()                # bounded waits that ran out inside a kernel
                 if is_log:
                     tps_wall = (self.tokens_seen - tokens0) / max(time.time() - start, 1e-9)
                     tps_dev = tokens_per_step / (ms / 1e3) if ms > 0 else float("nan")
