@@ -260,9 +260,15 @@ __global__ void __launch_bounds__(1024) rmsnorm_dw_reduce_kernel(const float* __
 
 // Number of blocks (= rows of the `partial` scratch) that lb_rmsnorm_bwd uses for this shape.
 extern "C" int lb_rmsnorm_bwd_blocks(int rows, int cols) {
-  (void)cols;
+  // as many blocks as are resident at once (one wave of the grid-stride loop): the block-per-row
+  // kernel fits 3 / 2 / 2 / 1 blocks per SM for 1 / 2 / 3 / 4 vectors per thread, the atomics
+  // version 2
+  const int nvec = cols / 8;
+  const int vpt = (nvec + 255) / 256;
+  const bool blk = vpt <= 4 && nvec % vpt == 0 && (nvec / vpt) % 32 == 0;
+  const int per_sm = !blk ? 2 : (vpt == 1 ? 3 : (vpt <= 3 ? 2 : 1));
   int blocks = (rows + 7) / 8;
-  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks > 148 * per_sm) blocks = 148 * per_sm;
   return blocks < 1 ? 1 : blocks;
 }
 

@@ -153,8 +153,12 @@ class DistributedAdamW:
             self.master[b.shard_off:b.shard_off + b.shard_len].copy_(src.float())
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
-        self.grad_shard = torch.zeros(shard_off, dtype=flat.dtype, device=self.device)
-        self.param_shard = torch.empty(shard_off, dtype=flat.dtype, device=self.device)
+        if all(b.n == 1 and b.shard_off == b.start for b in self.buckets) and shard_off == flat.numel():
+            # no replicas: the "shards" are the arenas themselves (saves two full-arena copies per step)
+            self.grad_shard, self.param_shard = self.flat_grads, self.flat_params
+        else:
+            self.grad_shard = torch.zeros(shard_off, dtype=flat.dtype, device=self.device)
+            self.param_shard = torch.empty(shard_off, dtype=flat.dtype, device=self.device)
         # ---- hooks for overlapped reduction ----
         self.sync_enabled = True
         self.overlap = overlap and flat.is_cuda and any(b.n > 1 for b in self.buckets) and self.fused_dp is None
@@ -224,7 +228,8 @@ class DistributedAdamW:
         g = self.flat_grads[b.start:b.end]
         out = self.grad_shard[b.shard_off:b.shard_off + b.shard_len]
         if b.n == 1:
-            out.copy_(g)
+            if out.data_ptr() != g.data_ptr():
+                out.copy_(g)
             return
         if async_op and self.comm_stream is not None:
             self.comm_stream.wait_stream(torch.cuda.current_stream())
@@ -320,7 +325,8 @@ class DistributedAdamW:
             src = self.param_shard[b.shard_off:b.shard_off + b.shard_len]
             dst = self.flat_params[b.start:b.end]
             if b.n == 1:
-                dst.copy_(src)
+                if dst.data_ptr() != src.data_ptr():
+                    dst.copy_(src)
             else:
                 dist.all_gather_into_tensor(dst, src, group=b.group)
         self._reset_buckets()
