@@ -72,9 +72,9 @@ __device__ __forceinline__ void give_up(volatile int* abort_flag, unsigned where
 }
 
 // One tile of the producer / of the MMA issuer, specialised on the operand majors: with the majors
-// as compile-time constants every descriptor field and the number of TMA boxes is a constant, so the
-// single-thread issue loops stay on the uniform datapath although the tile itself comes from a list
-// in memory.
+// as compile-time constants every descriptor field and the number of TMA boxes is a constant (with
+// run-time majors the producer issued predicated-off TMA instructions for the branch not taken and
+// the tensor pipe lost a fifth of its activity), although the tile itself comes from a list in memory.
 template <bool A_MN, bool B_MN>
 __device__ __forceinline__ bool produce_tile(const CUtensorMap* ta, const CUtensorMap* tb, int m0, int n0, int num_kb,
                                              uint32_t smem_base, uint32_t bar_base, int& stage, uint32_t& phase,

@@ -232,8 +232,8 @@ __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.
 __device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // One tile of the producer / of the MMA issuer with the operand majors as compile-time constants:
-// descriptor fields and the number of TMA boxes become constants and the single-thread issue loops
-// stay on the uniform datapath (measured 3-8 % faster than run-time majors).
+// descriptor fields and the number of TMA boxes become constants in the single-thread issue loops
+// (measured 3-8 % faster than run-time majors).
 template <int NSTAGES, bool A_MN, bool B_MN>
 __device__ __forceinline__ bool produce_tile(const CUtensorMap* ta, const CUtensorMap* tb, int m0, int n0, int num_kb,
                                              uint32_t smem_base, uint32_t bar_base, int& stage, uint32_t& phase,
