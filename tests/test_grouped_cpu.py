@@ -119,3 +119,35 @@ def test_grouped_linear_segments_match_per_segment_math():
     y.square().sum().backward()
     assert groups[1][0].grad is None or groups[1][0].grad.abs().max().item() == 0
     assert x.grad[9:].abs().max().item() == 0 and x.grad[:9].abs().max().item() > 0
+
+
+def test_bucket_hook_counts_each_parameter_once_and_skips_pending_or_unsynced():
+    from lightron_b200 import mesh
+    from lightron_b200.config import ModelArgs
+    from lightron_b200.models import LightronTransformer, init_weights
+    from lightron_b200.optim import DistributedAdamW
+    mesh.set_context(None)
+    args = ModelArgs(dim=32, n_layers=1, n_heads=2, n_kv_heads=2, vocab_size=64, intermediate_size=64, max_seq_len=16)
+    m = LightronTransformer(args, dtype=torch.float32, device=torch.device("cpu"))
+    init_weights(m, 0)
+    opt = DistributedAdamW(m, lr=1e-3)
+    assert opt.grad_shard.data_ptr() == opt.flat_grads.data_ptr()        # no replicas: shards alias the arenas
+    b = opt.buckets[0]
+    launched = []
+    opt._launch_reduce = lambda bb, async_op: launched.append(bb)
+    hook = opt._make_hook(b)
+    p0, p1 = opt.params[0], opt.params[1]
+    b.pending, b.seen = 2, set()
+    hook(p0); hook(p0)                                   # by hand and again by autograd: one count
+    assert b.pending == 1 and not launched
+    p1._lb_wgrad_pending = True
+    hook(p1)                                             # its weight gradient is still queued
+    assert b.pending == 1
+    p1._lb_wgrad_pending = False
+    with opt.no_sync():
+        hook(p1)                                         # micro-batch without gradient sync
+    assert b.pending == 1
+    hook(p1)
+    assert b.pending == 0 and launched == [b]
+    opt._reset_buckets()
+    assert b.pending == b.n_params and not b.seen
