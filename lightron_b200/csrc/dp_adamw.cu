@@ -10,7 +10,7 @@
 //   3. stores the new bf16 parameters into every replica's parameter arena with 16-byte peer
 //      stores (the all-gather).
 // The whole GPU takes part (hundreds of thousands of independent 16-byte loads in flight cover
-// the NVLink latency).  Two flag rounds frame the kernel: "my gradients are complete" before any
+// the NVLink latency).  Two flag exchanges frame the kernel: "my gradients are complete" before any
 // peer load, and "my parameter pushes have landed" before the kernel may end, so that the next
 // forward on this stream sees every shard.  Waits are bounded and report through lb_dp_status().
 #include "common.cuh"
@@ -60,7 +60,7 @@ __device__ __forceinline__ bool wait_ge(const unsigned int* f, unsigned int targ
 }
 
 __global__ void __launch_bounds__(256) dp_adamw_kernel(const DpParams p) {
-  // ---- round 1: gradients of every replica are complete ----
+  // ---- first flag exchange: gradients of every replica are complete ----
   if (blockIdx.x == 0 && threadIdx.x < p.n) {
     __threadfence_system();
     st_release_sys(p.flags[threadIdx.x] + p.rank, p.epoch);
@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(256) dp_adamw_kernel(const DpParams p) {
     for (int r = 0; r < p.n; r++) *reinterpret_cast<uint4*>(p.param[r] + e) = packed;
   }
 
-  // ---- round 2: my pushes have landed everywhere; leave only when everybody's have ----
+  // ---- second flag exchange: my pushes have landed everywhere; leave only when everybody's have ----
   __threadfence_system();
   __syncthreads();
   __shared__ unsigned int s_last;
