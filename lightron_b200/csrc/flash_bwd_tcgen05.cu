@@ -12,19 +12,25 @@
 // the columns) read S and dP with tcgen05.ld, form P = exp(scale S - lse) and
 // dS = P (dP - delta) scale in registers, and write both as bf16 into 128B-swizzled shared
 // memory, where the same bytes serve as K-major (dQ) and MN-major (dV, dK) MMA operands.
-// Each dQ tile goes TMEM -> registers -> a per-warp staging area -> one asynchronous bulk
-// reduce-add (cp.reduce.async.bulk .add.f32) per warp into an fp32 accumulator in global memory
-// whose layout is the staging layout (un-permuted by the final convert kernel), so no atomic
-// instructions pass through the load/store pipe.
+// The gradient MMAs of a query block run in the order dQ, dV, dK: with head_dim 64 each dQ tile
+// goes TMEM -> registers -> a per-warp staging area -> one asynchronous bulk reduce-add
+// (cp.reduce.async.bulk .add.f32) per warp into an fp32 accumulator in global memory while dV and dK
+// are still on the tensor pipe, so the drain (about 1200 cycles with its proxy fence) is off the
+// critical path.  The accumulator's layout is the staging layout (un-permuted by the final convert
+// kernel), so no atomic instructions pass through the load/store pipe.
 // Warp roles (576 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-17 math.
-// With head_dim 128 the dQ tile aliases the dP columns (TMEM is 512 columns) and Q/dO are
-// single-buffered; with head_dim 64 Q/dO are double-buffered and S/dP of the next query block
-// are issued while the current one is still in the math warps.
+// With head_dim 128 the dQ tile aliases the dP columns (TMEM is 512 columns), Q has two stages and
+// dO one; with head_dim 64 Q and dO have three stages each and S/dP of the next query block are
+// issued while the current one is still in the math warps.
 // All waits are bounded; on expiry a status word is set and the CTA drains and frees its TMEM.
 #include <stdlib.h>
 #include "tcgen05.cuh"
 
 static __device__ unsigned int g_fab_status[4] = {0, 0, 0, 0};
+// Developer instrumentation (build with -DLB_FA_PROFILE): summed cycles per phase, see lb_flash_bwd_prof().
+#ifdef LB_FA_PROFILE
+static __device__ unsigned long long g_fab_prof[16];
+#endif
 
 namespace {
 using namespace bw;
@@ -44,7 +50,13 @@ struct FaBwdParams {
 template <int D>
 struct BwdCfg {
   static constexpr int BM = 128, BN = 128;
-  static constexpr int ST = (D == 64) ? 2 : 1;          // Q/dO stages
+  // Q and dO go through separate stage rings.  head_dim 64: three stages each, so the loads of
+  // query block i+1 are in flight while the gradient MMAs of block i-1 still read their stage
+  // (with fewer stages the issuer was measured waiting 1450 cycles per block on TMA latency).
+  // head_dim 128 (shared memory is short): one stage each; the gradient MMAs run in the order
+  // dQ, dV, dK, so dO's stage is released while dK is still running.
+  static constexpr int QS = (D == 64) ? 3 : 1;
+  static constexpr int DS = (D == 64) ? 3 : 1;
   static constexpr bool EARLY = (D == 64);              // issue S/dP of block i+1 before dV/dK/dQ of block i
   static constexpr int ATOMS = D / 64;
   static constexpr int ATOM_BYTES = 128 * 128;
@@ -56,14 +68,14 @@ struct BwdCfg {
   static constexpr bool STG_ALIAS = (D == 128);         // staging shares the P/dS bytes when smem is short
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + TILE_BYTES;
-  static constexpr int OFF_Q = OFF_V + TILE_BYTES;              // [ST]
-  static constexpr int OFF_DO = OFF_Q + ST * TILE_BYTES;        // [ST]
-  static constexpr int OFF_P = OFF_DO + ST * TILE_BYTES;
+  static constexpr int OFF_Q = OFF_V + TILE_BYTES;              // [QS]
+  static constexpr int OFF_DO = OFF_Q + QS * TILE_BYTES;        // [DS]
+  static constexpr int OFF_P = OFF_DO + DS * TILE_BYTES;
   static constexpr int OFF_DS = OFF_P + P_BYTES;
   static constexpr int OFF_STG = STG_ALIAS ? OFF_P : OFF_DS + P_BYTES;
   static constexpr int OFF_BAR = STG_ALIAS ? OFF_DS + P_BYTES : OFF_STG + STG_BYTES;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
-  static constexpr int NBAR = 1 + 2 * ST + 6;
+  static constexpr int NBAR = 1 + 2 * QS + 2 * DS + 7;
   static constexpr int NTHREADS = 576;
   // TMEM columns
   static constexpr int COL_S = 0, COL_DP = 128;
@@ -151,11 +163,13 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t kv_full = bar0;
-  auto qdo_full = [&](int s) { return bar0 + 8u * (1 + s); };
-  auto qdo_empty = [&](int s) { return bar0 + 8u * (1 + C::ST + s); };
-  const uint32_t bar1 = bar0 + 8u * (1 + 2 * C::ST);
+  auto q_full = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto q_empty = [&](int s) { return bar0 + 8u * (1 + C::QS + s); };
+  auto do_full = [&](int s) { return bar0 + 8u * (1 + 2 * C::QS + s); };
+  auto do_empty = [&](int s) { return bar0 + 8u * (1 + 2 * C::QS + C::DS + s); };
+  const uint32_t bar1 = bar0 + 8u * (1 + 2 * C::QS + 2 * C::DS);
   const uint32_t sdp_full = bar1, sdp_free = bar1 + 8, pds_full = bar1 + 16, dq_full = bar1 + 24, dq_free = bar1 + 32,
-                 stg_free = bar1 + 40;
+                 pds_free = bar1 + 40, stg_free = bar1 + 48;
 
   const int nblk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int n0 = nblk * C::BN;
@@ -173,12 +187,14 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   if (threadIdx.x == 0) {
     s_abort = 0;
     mbar_init(kv_full, 1);
-    for (int s = 0; s < C::ST; s++) { mbar_init(qdo_full(s), 1); mbar_init(qdo_empty(s), 1); }
+    for (int s = 0; s < C::QS; s++) { mbar_init(q_full(s), 1); mbar_init(q_empty(s), 1); }
+    for (int s = 0; s < C::DS; s++) { mbar_init(do_full(s), 1); mbar_init(do_empty(s), 1); }
     mbar_init(sdp_full, 1);
     mbar_init(sdp_free, 512);
     mbar_init(pds_full, 512);
     mbar_init(dq_full, 1);
     mbar_init(dq_free, 512);
+    mbar_init(pds_free, 1);
     mbar_init(stg_free, 16);
     mbar_init_fence();
     prefetch_tmap(&tq); prefetch_tmap(&tk); prefetch_tmap(&tv); prefetch_tmap(&tdo);
@@ -201,16 +217,19 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       }
       bool ok = true;
       for (int it = 0; it < total_it; it++) {
-        const int st = it % C::ST;
+        const int qs = it % C::QS, ds = it % C::DS;
         const int h = hk * rep + it / per_head;
         const int m0 = (mb_first + it % per_head) * C::BM;
-        if (!mbar_wait(qdo_empty(st), (((uint32_t)(it / C::ST)) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-        mbar_expect_tx(qdo_full(st), 2 * C::TILE_BYTES);
+        if (!mbar_wait(q_empty(qs), (((uint32_t)(it / C::QS)) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(q_full(qs), C::TILE_BYTES);
 #pragma unroll
-        for (int a = 0; a < C::ATOMS; a++) {
-          tma_load_2d(sbase + C::OFF_Q + st * C::TILE_BYTES + a * C::ATOM_BYTES, &tq, h * D + a * 64, b * p.Sq + m0, qdo_full(st));
-          tma_load_2d(sbase + C::OFF_DO + st * C::TILE_BYTES + a * C::ATOM_BYTES, &tdo, h * D + a * 64, b * p.Sq + m0, qdo_full(st));
-        }
+        for (int a = 0; a < C::ATOMS; a++)
+          tma_load_2d(sbase + C::OFF_Q + qs * C::TILE_BYTES + a * C::ATOM_BYTES, &tq, h * D + a * 64, b * p.Sq + m0, q_full(qs));
+        if (!mbar_wait(do_empty(ds), (((uint32_t)(it / C::DS)) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(do_full(ds), C::TILE_BYTES);
+#pragma unroll
+        for (int a = 0; a < C::ATOMS; a++)
+          tma_load_2d(sbase + C::OFF_DO + ds * C::TILE_BYTES + a * C::ATOM_BYTES, &tdo, h * D + a * 64, b * p.Sq + m0, do_full(ds));
       }
       if (!ok) atomicExch(&g_fab_status[0], 1u);
     }
@@ -227,64 +246,62 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       const uint64_t mK = make_desc(sbase + C::OFF_K, C::ATOM_BYTES, 1024);
       const uint64_t mQ = make_desc(sbase + C::OFF_Q, C::ATOM_BYTES, 1024), mDO = make_desc(sbase + C::OFF_DO, C::ATOM_BYTES, 1024);
       const uint64_t mP = make_desc(sbase + C::OFF_P, C::ATOM_BYTES, 1024), mDS = make_desc(sbase + C::OFF_DS, C::ATOM_BYTES, 1024);
-      auto issue_s_dp = [&](int st) {
-        const uint64_t so = (uint64_t)((st * C::TILE_BYTES) >> 4);
+      // S and dP of query block `it`: needs its Q / dO stages and the S / dP columns (held by the
+      // math warps until they have block it-1 in registers; with head_dim 128 dQ of block it-1
+      // sits in the dP columns until it has been drained)
+      auto issue_s_dp = [&](int it) -> bool {
+        const int qs = it % C::QS, ds = it % C::DS;
+        if (!mbar_wait(q_full(qs), ((uint32_t)(it / C::QS)) & 1u, abort_flag)) return false;
+        if (!mbar_wait(do_full(ds), ((uint32_t)(it / C::DS)) & 1u, abort_flag)) return false;
+        if (it > 0 && !mbar_wait(C::EARLY ? sdp_free : dq_free, (uint32_t)(it - 1) & 1u, abort_flag)) return false;
+        fence_after();
+        const uint64_t qo = (uint64_t)((qs * C::TILE_BYTES) >> 4), go = (uint64_t)((ds * C::TILE_BYTES) >> 4);
 #pragma unroll
         for (int s = 0; s < D / 16; s++) {
           const uint64_t o = (uint64_t)(((s >> 2) * C::ATOM_BYTES + (s & 3) * 32) >> 4);
-          umma_bf16(tmem_base + C::COL_S, kQ + so + o, kK + o, idesc_s, s ? 1u : 0u);
+          umma_bf16(tmem_base + C::COL_S, kQ + qo + o, kK + o, idesc_s, s ? 1u : 0u);
         }
 #pragma unroll
         for (int s = 0; s < D / 16; s++) {
           const uint64_t o = (uint64_t)(((s >> 2) * C::ATOM_BYTES + (s & 3) * 32) >> 4);
-          umma_bf16(tmem_base + C::COL_DP, kDO + so + o, kV + o, idesc_s, s ? 1u : 0u);
+          umma_bf16(tmem_base + C::COL_DP, kDO + go + o, kV + o, idesc_s, s ? 1u : 0u);
         }
         umma_commit(sdp_full);
+        return true;
       };
-      auto issue_grads = [&](int st, int it) {
-        const uint64_t so = (uint64_t)((st * C::TILE_BYTES) >> 4);
+      // dQ first: its tile can leave for global memory while dV and dK are still on the tensor
+      // pipe.  dV releases the dO stage, dK the Q stage and the P / dS bytes.
+      auto issue_grads = [&](int it) -> bool {
+        const int qs = it % C::QS, ds = it % C::DS;
+        if (!mbar_wait(pds_full, (uint32_t)it & 1u, abort_flag)) return false;
+        if (C::EARLY && it > 0 && !mbar_wait(dq_free, (uint32_t)(it - 1) & 1u, abort_flag)) return false;
+        fence_after();
+        const uint64_t qo = (uint64_t)((qs * C::TILE_BYTES) >> 4), go = (uint64_t)((ds * C::TILE_BYTES) >> 4);
         const uint32_t acc0 = it ? 1u : 0u;
-        umma_bf16(tmem_base + C::COL_DV, mP, mDO + so, idesc_kv, acc0);       // dV += P^T dO   (K = 128 queries)
-#pragma unroll
-        for (int s = 1; s < C::BM / 16; s++)
-          umma_bf16(tmem_base + C::COL_DV, mP + (uint64_t)(s * 128), mDO + so + (uint64_t)(s * 128), idesc_kv, 1u);
-        umma_bf16(tmem_base + C::COL_DK, mDS, mQ + so, idesc_kv, acc0);       // dK += dS^T Q
-#pragma unroll
-        for (int s = 1; s < C::BM / 16; s++)
-          umma_bf16(tmem_base + C::COL_DK, mDS + (uint64_t)(s * 128), mQ + so + (uint64_t)(s * 128), idesc_kv, 1u);
 #pragma unroll
         for (int s = 0; s < C::BN / 16; s++)                                   // dQ = dS K      (K = 128 keys)
           umma_bf16(tmem_base + C::COL_DQ, kDS + (uint64_t)(((s >> 2) * C::ATOM_BYTES + (s & 3) * 32) >> 4),
                     mK + (uint64_t)(s * 128), idesc_dq, s ? 1u : 0u);
         umma_commit(dq_full);
-        umma_commit(qdo_empty(st));
+        umma_bf16(tmem_base + C::COL_DV, mP, mDO + go, idesc_kv, acc0);       // dV += P^T dO   (K = 128 queries)
+#pragma unroll
+        for (int s = 1; s < C::BM / 16; s++)
+          umma_bf16(tmem_base + C::COL_DV, mP + (uint64_t)(s * 128), mDO + go + (uint64_t)(s * 128), idesc_kv, 1u);
+        umma_commit(do_empty(ds));
+        umma_bf16(tmem_base + C::COL_DK, mDS, mQ + qo, idesc_kv, acc0);       // dK += dS^T Q
+#pragma unroll
+        for (int s = 1; s < C::BM / 16; s++)
+          umma_bf16(tmem_base + C::COL_DK, mDS + (uint64_t)(s * 128), mQ + qo + (uint64_t)(s * 128), idesc_kv, 1u);
+        umma_commit(q_empty(qs));
+        umma_commit(pds_free);
+        return true;
       };
       bool ok = mbar_wait(kv_full, 0, abort_flag);
-      if (ok) ok = mbar_wait(qdo_full(0), 0, abort_flag);
-      if (ok) {
-        fence_after();
-        issue_s_dp(0);
-      }
+      if (ok) ok = issue_s_dp(0);
       for (int it = 0; it < total_it && ok; it++) {
-        const int st = it % C::ST;
-        if (C::EARLY && it + 1 < total_it) {
-          const int st1 = (it + 1) % C::ST;
-          if (!mbar_wait(qdo_full(st1), ((uint32_t)((it + 1) / C::ST)) & 1u, abort_flag)) { ok = false; break; }
-          if (!mbar_wait(sdp_free, (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
-          fence_after();
-          issue_s_dp(st1);
-        }
-        if (!mbar_wait(pds_full, (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
-        if (it > 0 && !mbar_wait(dq_free, (uint32_t)(it - 1) & 1u, abort_flag)) { ok = false; break; }
-        fence_after();
-        issue_grads(st, it);
-        if (!C::EARLY && it + 1 < total_it) {
-          const int st1 = (it + 1) % C::ST;
-          if (!mbar_wait(qdo_full(st1), ((uint32_t)((it + 1) / C::ST)) & 1u, abort_flag)) { ok = false; break; }
-          if (!mbar_wait(dq_free, (uint32_t)it & 1u, abort_flag)) { ok = false; break; }   // dQ aliases dP
-          fence_after();
-          issue_s_dp(st1);
-        }
+        if (C::EARLY && it + 1 < total_it) ok = issue_s_dp(it + 1);
+        if (ok) ok = issue_grads(it);
+        if (!C::EARLY && ok && it + 1 < total_it) ok = issue_s_dp(it + 1);
       }
       if (!ok) atomicExch(&g_fab_status[0], 2u);
     }
@@ -293,19 +310,23 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     const int quad = warp & 3;
     const int part = (warp - 2) >> 2;               // which 32 of the 128 key columns / which quarter of d
     const int rit = quad * 32 + lane;               // row inside the 128-row tile
-    const int ws = part * 4 + quad;                 // this warp's slot in the dQ staging / accumulator layout
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     const float sl2 = p.scale * 1.4426950408889634f;
     const float l2e = 1.4426950408889634f;
     uint8_t* sProw = smem + C::OFF_P + (part >> 1) * C::ATOM_BYTES;
     uint8_t* sDSrow = smem + C::OFF_DS + (part >> 1) * C::ATOM_BYTES;
-    uint8_t* stg = smem + C::OFF_STG + ws * C::STG_WARP;
     constexpr int DQC = C::DQC;
     bool ok = true;
     int prev_m0 = 0, prev_h = 0;
+    const int ws = part * 4 + quad;                 // this warp's slot in the dQ staging / accumulator layout
+    uint8_t* stg = smem + C::OFF_STG + ws * C::STG_WARP;
+    const int n_mblocks_acc = n_mblocks;
     int n_flushed = 0;
+    // dQ of query block `it_prev`: TMEM -> registers -> this warp's staging area -> one asynchronous
+    // bulk reduce-add into the fp32 accumulator (whose layout is the staging layout).  Reduce-adds
+    // issued from registers (red.global.add.v4.f32) were measured slower: the warps stall on the
+    // load/store pipe, while the bulk engine drains in the background.
     auto flush_dq = [&](int it_prev) -> bool {
-      // dQ of query block `it_prev`: TMEM -> registers -> staging -> bulk reduce-add to global
       if (!mbar_wait(dq_full, (uint32_t)it_prev & 1u, abort_flag)) return false;
       fence_after();
       uint32_t r[DQC];
@@ -313,7 +334,10 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       tmem_ld_wait();
       fence_before();
       mbar_arrive(dq_free);
-      if (!C::STG_ALIAS) {
+      if (C::STG_ALIAS) {
+        // the staging bytes are the P / dS bytes: dV and dK must have finished reading them
+        if (!mbar_wait(pds_free, (uint32_t)it_prev & 1u, abort_flag)) return false;
+      } else {
         if (lane == 0) bulk_wait_read();            // this warp's previous bulk op has read the staging area
         __syncwarp();
       }
@@ -324,7 +348,7 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        float* dst = p.dq_acc + (((long long)b * p.hq + prev_h) * n_mblocks + (prev_m0 >> 7)) * (128 * D) +
+        float* dst = p.dq_acc + (((long long)b * p.hq + prev_h) * n_mblocks_acc + (prev_m0 >> 7)) * (128 * D) +
                      (long long)ws * (32 * DQC);
         bulk_reduce_add_f32(dst, smem_u32(stg), C::STG_WARP);
         bulk_commit();
@@ -375,14 +399,13 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         pp[i >> 1] = *reinterpret_cast<uint32_t*>(&pb);
         dd[i >> 1] = *reinterpret_cast<uint32_t*>(&db);
       }
-      // P/dS smem may be rewritten only after the previous block's dV/dK/dQ MMAs have read it; the
-      // dq_full wait inside flush_dq() of that block guarantees it in both schedules.
       if (C::EARLY && it > 0) {
         if (!flush_dq(it - 1)) { ok = false; break; }
       }
-      if (C::STG_ALIAS && it > 0) {                  // every warp's bulk op has finished reading the shared bytes
-        if (!mbar_wait(stg_free, (uint32_t)(it - 1) & 1u, abort_flag)) { ok = false; break; }
-      }
+      // P / dS bytes may be rewritten once dV, dK and dQ of the previous block have read them
+      // (and, where the dQ staging shares them, once every warp's bulk op has read its staging)
+      if (it > 0 && !mbar_wait(pds_free, (uint32_t)(it - 1) & 1u, abort_flag)) { ok = false; break; }
+      if (C::STG_ALIAS && it > 0 && !mbar_wait(stg_free, (uint32_t)(it - 1) & 1u, abort_flag)) { ok = false; break; }
 #pragma unroll
       for (int c = 0; c < 4; c++) {
         const uint32_t o = sw128_off(rit, (part & 1) * 4 + c);
@@ -399,8 +422,9 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     }
     if (C::EARLY && ok && total_it > 0) ok = flush_dq(total_it - 1);
     if (lane == 0 && n_flushed > 0) bulk_wait_read();   // staging must outlive the last bulk read
+    if (ok && total_it > 0) ok = mbar_wait(pds_free, (uint32_t)(total_it - 1) & 1u, abort_flag);   // every MMA has finished
     if (ok && total_it > 0) {
-      // dq_full of the last block was committed after every MMA: dV and dK are final
+      fence_after();
       const int key = n0 + rit;
       bf16* dkrow = p.dk + ((long long)b * p.Sk + key) * p.dk_ts + (long long)hk * D + part * DQC;
       bf16* dvrow = p.dv + ((long long)b * p.Sk + key) * p.dv_ts + (long long)hk * D + part * DQC;
@@ -486,6 +510,15 @@ extern "C" int lb_flash_bwd_status(void* out) {
   cudaMemcpyToSymbol(g_fab_status, zeros, sizeof(zeros));
   return LB_OK;
 }
+
+#ifdef LB_FA_PROFILE
+extern "C" int lb_flash_bwd_prof(void* out) {
+  cudaMemcpyFromSymbol(out, g_fab_prof, sizeof(unsigned long long) * 16);
+  unsigned long long zeros[16] = {0};
+  cudaMemcpyToSymbol(g_fab_prof, zeros, sizeof(zeros));
+  return LB_OK;
+}
+#endif
 
 // Same contract as lb_flash_bwd (flash_attn.cu) except for the scratch: dq_acc is zero-initialised
 // fp32 of B * hq * ceil(Sq/128) * 128 * d elements (tile-permuted layout, see fa_dq_convert_kernel);

@@ -4,18 +4,36 @@
 // the tensor pipe.  Per 128-key block:
 //     S_t = Q_t K^T          tcgen05.mma, 128x128xd, operands in 128B-swizzled smem (TMA), D in TMEM
 //     softmax(S_t)           one thread per query row reads its row straight from TMEM
-//                            (tcgen05.ld), so max / sum need no shuffles; P_t goes to smem as bf16
-//     O_t (+)= P_t V         tcgen05.mma, 128 x d x 128, V is the MN-major B operand as it sits in memory
+//                            (tcgen05.ld), so max / sum need no shuffles; P_t goes back to TMEM as
+//                            packed bf16 pairs (tcgen05.st)
+//     O_t (+)= P_t V         tcgen05.mma with the A operand in TMEM, 128 x d x 128, V is the MN-major
+//                            B operand as it sits in memory
+// P never touches shared memory: with P staged there the kernel was bound by shared-memory
+// bandwidth (128 B/clk: the P stores, the A-operand reads of P V and of Q K^T, the TMA writes),
+// measured as tcgen05.mma issue blocking for 400 / 620 cycles per S / P V group at head_dim 64.
 // O_t stays in TMEM for the whole key loop; when a row maximum grows the softmax threads rescale
 // it in place (tcgen05.ld / st) before the next P V is issued.
-// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-5
-// softmax of tile 0, warps 6-9 softmax of tile 1.  While one tile is in softmax the tensor pipe
+// Warp roles (384 threads): warp 0 TMA producer, warps 1 / 2 MMA issuers of tile 0 / 1 (warp 1
+// owns the TMEM allocation), warp 3 idle, warps 4-7 softmax of tile 0, warps 8-11 softmax of tile 1.
+// The two tiles run half a period apart (tile 1 starts late on purpose): the exponentials of one
+// then overlap the loads, maxima and waits of the other instead of queueing on the same MUFU unit.  While one tile is in softmax the tensor pipe
 // works on the other.  Layout / masking conventions are those of flash_attn.cu.
 // All waits are bounded; on expiry a status word is set and the CTA drains and frees its TMEM.
 #include <string.h>
 #include "tcgen05.cuh"
 
 static __device__ unsigned int g_fa_status[4] = {0, 0, 0, 0};
+
+// Developer instrumentation (build with -DLB_FA_PROFILE): cycles that lane 0 of every softmax warp
+// spends in each phase of the key-block loop, summed over the grid.  lb_flash_prof() reads and clears.
+#ifdef LB_FA_PROFILE
+static __device__ unsigned long long g_fa_prof[16];
+#define FA_T(i) const long long tp##i = clock64()
+#define FA_ACC(slot, a, b) prof[slot] += (unsigned long long)(tp##b - tp##a)
+#else
+#define FA_T(i)
+#define FA_ACC(slot, a, b)
+#endif
 
 namespace {
 using namespace bw;
@@ -72,23 +90,30 @@ __device__ __forceinline__ bool fa_flag_wait(const unsigned int* f, unsigned int
 template <int D>
 struct FaCfg {
   static constexpr int BM = 128, BN = 128;
-  static constexpr int KS = 2;
-  static constexpr int VS = (D == 64) ? 2 : 1;
+  static constexpr int KS = (D == 64) ? 3 : 2;
+  static constexpr int VS = (D == 64) ? 3 : 1;
   static constexpr int ATOMS = D / 64;
   static constexpr int ATOM_BYTES = 128 * 128;          // 128 rows x 128 B
   static constexpr int TILE_BYTES = ATOMS * ATOM_BYTES; // one Q / K / V tile
-  static constexpr int P_BYTES = 2 * ATOM_BYTES;        // 128 x 128 bf16
+  // TMEM columns: S_t fp32 [128], O_t fp32 [D], P_t packed bf16 [64].  With head_dim 64 all six
+  // regions fit in the 512 columns and P never touches shared memory.  With head_dim 128 S and O
+  // fill the 512 columns: P_t is staged in shared memory instead (letting P_t take columns of S_t
+  // was measured slower: S_t of the next key block then has to queue behind P_t V).
+  static constexpr bool P_TMEM = (D == 64);
+  static constexpr int COL_S = 0, COL_O = 256, COL_P = 384;
+  static constexpr int P_STRIDE = 64;
+  static constexpr int P_BYTES = 2 * ATOM_BYTES;        // 128 x 128 bf16 (shared-memory variant)
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + 2 * TILE_BYTES;
   static constexpr int OFF_V = OFF_K + KS * TILE_BYTES;
   static constexpr int OFF_P = OFF_V + VS * TILE_BYTES;
-  static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
+  static constexpr int OFF_BAR = OFF_P + (P_TMEM ? 0 : 2 * P_BYTES);
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
   static constexpr int NBAR = 1 + 2 * KS + 2 * VS + 8;
 };
 
 template <int D>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(384, 1)
 fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                  const __grid_constant__ CUtensorMap tv, const FaFwdParams p, const FaPush push) {
   using C = FaCfg<D>;
@@ -174,8 +199,8 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   if (threadIdx.x == 0) {
     s_abort = 0;
     mbar_init(q_full, 1);
-    for (int s = 0; s < C::KS; s++) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); }
-    for (int s = 0; s < C::VS; s++) { mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1); }
+    for (int s = 0; s < C::KS; s++) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 2); }
+    for (int s = 0; s < C::VS; s++) { mbar_init(v_full(s), 1); mbar_init(v_empty(s), 2); }
     for (int t = 0; t < 2; t++) { mbar_init(s_full(t), 1); mbar_init(p_full(t), 128); mbar_init(pv_done(t), 1); mbar_init(s_free(t), 128); }
     mbar_init_fence();
     prefetch_tmap(&tq); prefetch_tmap(&tk); prefetch_tmap(&tv);
@@ -221,125 +246,143 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       }
       if (!ok) atomicExch(&g_fa_status[0], 1u);
     }
-  } else if (warp == 1) {
-    // ------------------------------- MMA issuer -------------------------------
+  } else if (warp == 1 || warp == 2) {
+    // ------------------------------- MMA issuers -------------------------------
+    // One issuing thread per query tile.  A tcgen05.mma costs its issuer 60-90 cycles whatever its
+    // size (measured: 370 cycles for the four 128x128x16 of one S, 500 for the eight 128x64x16 of
+    // one P V), so a single thread feeding both tiles was the bottleneck of the whole kernel; two
+    // threads issue side by side and each follows the fixed order of its own tile with blocking
+    // waits: S(0); then per key block S(j+1) as soon as the softmax threads hold S(j) in registers,
+    // and P(j) V as soon as P(j) is in TMEM (or, head_dim 128, in shared memory).
+    // A K / V stage is free once BOTH tiles have used it, so each thread arrives on the stage's
+    // empty barrier for every block, also for blocks its own tile does not need.
+    const int t = warp - 1;
     if (lane == 0 && nb_max > 0) {
       const uint32_t idesc_s = make_idesc(C::BM, C::BN, 0, 0);
       const uint32_t idesc_o = make_idesc(C::BM, D, 0, 1);
-      // descriptor bases; a tile / stage / k-step only changes the 16-byte-granular start address
-      const uint64_t dq0 = make_desc(sbase + C::OFF_Q, 16, 1024);
+      // descriptor bases; a stage / k-step only changes the 16-byte-granular start address
+      const uint64_t qa = make_desc(sbase + C::OFF_Q + t * C::TILE_BYTES, 16, 1024);
       const uint64_t dk0 = make_desc(sbase + C::OFF_K, 16, 1024);
-      const uint64_t dp0 = make_desc(sbase + C::OFF_P, 16, 1024);
       const uint64_t dv0 = make_desc(sbase + C::OFF_V, C::ATOM_BYTES, 1024);
-      auto issue_s = [&](int t, int ks) {
-        const uint64_t qa = dq0 + (uint64_t)((t * C::TILE_BYTES) >> 4);
+      const uint32_t s_dst = tmem_base + C::COL_S + t * C::BN;
+      const uint32_t o_dst = tmem_base + C::COL_O + t * D;
+      const uint32_t pa = tmem_base + C::COL_P + t * C::P_STRIDE;          // 8 columns per K = 16 slice
+      const uint64_t dp0 = make_desc(sbase + C::OFF_P + t * C::P_BYTES, 16, 1024);
+      const int n_my = nb[t];
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      auto issue_s = [&](int j) -> bool {             // S(j) = Q K(j)^T, then release K(j)'s stage
+        const int ks = j % C::KS;
+        if (!mbar_wait(k_full(ks), ((uint32_t)(j / C::KS)) & 1u, abort_flag)) return false;
+        fence_after();
         const uint64_t ka = dk0 + (uint64_t)((ks * C::TILE_BYTES) >> 4);
-        const uint32_t dst = tmem_base + t * C::BN;
 #pragma unroll
         for (int s = 0; s < D / 16; s++) {
           const uint64_t o = (uint64_t)(((s >> 2) * C::ATOM_BYTES + (s & 3) * 32) >> 4);
-          umma_bf16(dst, qa + o, ka + o, idesc_s, s ? 1u : 0u);
+          umma_bf16(s_dst, qa + o, ka + o, idesc_s, s ? 1u : 0u);
         }
         umma_commit(s_full(t));
+        umma_commit(k_empty(ks));
+        return true;
       };
-      auto issue_pv = [&](int t, int vs, int j) {
-        const uint64_t pa = dp0 + (uint64_t)((t * C::P_BYTES) >> 4);
+      auto issue_pv = [&](int j) -> bool {            // O += P(j) V(j), then release V(j)'s stage
+        const int vs = j % C::VS;
+        if (!mbar_wait(p_full(t), (uint32_t)j & 1u, abort_flag)) return false;
+        if (!mbar_wait(v_full(vs), ((uint32_t)(j / C::VS)) & 1u, abort_flag)) return false;
+        fence_after();
         const uint64_t va = dv0 + (uint64_t)((vs * C::TILE_BYTES) >> 4);
-        const uint32_t dst = tmem_base + 2 * C::BN + t * D;
-        umma_bf16(dst, pa, va, idesc_o, j ? 1u : 0u);
+        if (C::P_TMEM) {
+          umma_bf16_ta(o_dst, pa, va, idesc_o, j ? 1u : 0u);
 #pragma unroll
-        for (int s = 1; s < C::BN / 16; s++)
-          umma_bf16(dst, pa + (uint64_t)(((s >> 2) * C::ATOM_BYTES + (s & 3) * 32) >> 4), va + (uint64_t)((s * 2048) >> 4),
-                    idesc_o, 1u);
+          for (int s = 1; s < C::BN / 16; s++)
+            umma_bf16_ta(o_dst, pa + 8u * s, va + (uint64_t)((s * 2048) >> 4), idesc_o, 1u);
+        } else {
+          umma_bf16(o_dst, dp0, va, idesc_o, j ? 1u : 0u);
+#pragma unroll
+          for (int s = 1; s < C::BN / 16; s++)
+            umma_bf16(o_dst, dp0 + (uint64_t)(((s >> 2) * C::ATOM_BYTES + (s & 3) * 32) >> 4), va + (uint64_t)((s * 2048) >> 4),
+                      idesc_o, 1u);
+        }
         umma_commit(pv_done(t));
+        umma_commit(v_empty(vs));
+        return true;
       };
-      bool ok = mbar_wait(q_full, 0, abort_flag);
-      // Event-driven issue: each tile has an S stream and a P V stream; whichever has its inputs
-      // ready goes next, so S of the next key block is usually in flight while softmax runs.
-      int sj[2] = {0, 0}, pj[2] = {0, 0};
-      int k_rel = 0, v_rel = 0;
-      uint32_t idle = 0;
-      while (ok && (pj[0] < nb[0] || pj[1] < nb[1])) {
-        bool progress = false;
-#pragma unroll
-        for (int t = 0; t < 2; t++) {
-          if (sj[t] < nb[t]) {
-            const int j = sj[t];
-            if (mbar_try_wait(k_full(j % C::KS), ((uint32_t)(j / C::KS)) & 1u) &&
-                (j == 0 || mbar_try_wait(s_free(t), (uint32_t)(j - 1) & 1u))) {
-              fence_after();
-              issue_s(t, j % C::KS);
-              sj[t]++;
-              progress = true;
-            }
-          }
-          while (k_rel < nb_max && (sj[0] > k_rel || k_rel >= nb[0]) && (sj[1] > k_rel || k_rel >= nb[1])) {
-            umma_commit(k_empty(k_rel % C::KS));
-            k_rel++;
-          }
-          if (pj[t] < nb[t]) {
-            const int j = pj[t];
-            if (mbar_try_wait(v_full(j % C::VS), ((uint32_t)(j / C::VS)) & 1u) && mbar_try_wait(p_full(t), (uint32_t)j & 1u)) {
-              fence_after();
-              issue_pv(t, j % C::VS, j);
-              pj[t]++;
-              progress = true;
-            }
-          }
-          while (v_rel < nb_max && (pj[0] > v_rel || v_rel >= nb[0]) && (pj[1] > v_rel || v_rel >= nb[1])) {
-            umma_commit(v_empty(v_rel % C::VS));
-            v_rel++;
-          }
+      // stagger: tile 1 starts once tile 0 holds its first S in registers (two tiles marching in
+      // step were measured to spend 2300 cycles per block together in the exponentials and then
+      // idle together; half a period apart each has the MUFU unit to itself)
+      if (ok && t == 1 && nb[0] > 0 && n_my > 0) ok = mbar_wait(s_free(0), 0u, abort_flag);
+      if (ok && n_my > 0) ok = issue_s(0);
+      for (int j = 0; j < n_my && ok; j++) {
+        if (j + 1 < n_my) {
+          ok = mbar_wait(s_free(t), (uint32_t)j & 1u, abort_flag);
+          if (ok) ok = issue_s(j + 1);
         }
-        if (progress) {
-          idle = 0;
-        } else if (++idle > WAIT_LIMIT || ((idle & 255u) == 0 && *abort_flag)) {
-          *abort_flag = 1;
-          ok = false;
-        }
+        if (ok) ok = issue_pv(j);
+      }
+      // blocks that only the other tile needs: keep the stage rings in step
+      for (int j = n_my; j < nb_max && ok; j++) {
+        ok = mbar_wait(k_full(j % C::KS), ((uint32_t)(j / C::KS)) & 1u, abort_flag);
+        if (ok) mbar_arrive(k_empty(j % C::KS));
+        if (ok) ok = mbar_wait(v_full(j % C::VS), ((uint32_t)(j / C::VS)) & 1u, abort_flag);
+        if (ok) mbar_arrive(v_empty(j % C::VS));
       }
       if (!ok) atomicExch(&g_fa_status[0], 2u);
     }
-  } else {
+  } else if (warp >= 4) {
     // ------------------------------- softmax warps -------------------------------
-    const int t = (warp - 2) >> 2;
+    const int t = (warp - 4) >> 2;
     const int quad = warp & 3;
     const int rit = quad * 32 + lane;              // row inside the tile
     const int row = m0 + t * C::BM + rit;          // query index inside the sequence
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const uint32_t ts_addr = lane_addr + t * C::BN;
-    const uint32_t to_addr = lane_addr + 2 * C::BN + t * D;
+    const uint32_t ts_addr = lane_addr + C::COL_S + t * C::BN;
+    const uint32_t to_addr = lane_addr + C::COL_O + t * D;
+    const uint32_t tp_addr = lane_addr + C::COL_P + t * C::P_STRIDE;
     uint8_t* sP = smem + C::OFF_P + t * C::P_BYTES;
     const float sl2 = p.scale * 1.4426950408889634f;
     float m_i = -INFINITY, l_i = 0.f;
     bool ok = true;
     const int n_my = nb[t];
+#ifdef LB_FA_PROFILE
+    unsigned long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#endif
     for (int j = 0; j < n_my; j++) {
+      FA_T(0);
       if (!mbar_wait(s_full(t), (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
       fence_after();
+      FA_T(1);
       uint32_t r[128];
-      tmem_ld32(ts_addr, r);
-      tmem_ld32(ts_addr + 32, r + 32);
-      tmem_ld32(ts_addr + 64, r + 64);
-      tmem_ld32(ts_addr + 96, r + 96);
-      tmem_ld_wait();
-      fence_before();
-      mbar_arrive(s_free(t));                       // S_t may be overwritten by the next key block
       const int c0 = j * C::BN;
       const int warp_row0 = m0 + t * C::BM + quad * 32;
       const bool need_mask = (c0 + C::BN > p.Sk) || (p.causal && (c0 + C::BN - 1 > warp_row0 + off));
       const int lim = (p.causal ? min(p.Sk - 1, row + off) : p.Sk - 1) - c0;   // last visible column of this block
-      float mx = -INFINITY;
-      if (need_mask) {
+      // the row arrives in two halves so that the maximum of the first overlaps the second load;
+      // four independent chains keep the 128 comparisons from serialising on their latency
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      tmem_ld32(ts_addr, r);
+      tmem_ld32(ts_addr + 32, r + 32);
+      tmem_ld_wait();
+      tmem_ld32(ts_addr + 64, r + 64);
+      tmem_ld32(ts_addr + 96, r + 96);
 #pragma unroll
-        for (int i = 0; i < 128; i++) {
-          if (i > lim) r[i] = 0xff800000u;           // -inf
-          mx = fmaxf(mx, __uint_as_float(r[i]));
+      for (int half = 0; half < 2; half++) {
+        if (half == 1) {
+          tmem_ld_wait();
+          fence_before();
+          mbar_arrive(s_free(t));                     // S_t may be overwritten by the next key block
         }
-      } else {
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 128; i++) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = half * 64; i < half * 64 + 64; i++) {
+            if (i > lim) r[i] = 0xff800000u;           // -inf
+            mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i]));
+          }
+        } else {
+#pragma unroll
+          for (int i = half * 64; i < half * 64 + 64; i++) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i]));
+        }
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      FA_T(2);
       // Lazy reference maximum: keep the old one unless the new maximum is more than 2^8 above
       // it, so that O and l rarely need rescaling (values stay below 2^8 relative to it).
       float m_new = fmaxf(m_i, mx);
@@ -347,7 +390,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       const float m_s = (m_new == -INFINITY) ? 0.f : m_new * sl2;
       const float corr = (m_i == -INFINITY) ? 0.f : exp2f(m_i * sl2 - m_s);
       if (j > 0) {
-        // previous P V finished: O is stable and the P buffer may be overwritten
+        // previous P V finished: O is stable and the P columns may be overwritten
         if (!mbar_wait(pv_done(t), (uint32_t)(j - 1) & 1u, abort_flag)) { ok = false; break; }
         fence_after();
         if (__any_sync(0xffffffffu, m_new != m_i)) {
@@ -363,30 +406,48 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
           tmem_st_wait();
         }
       }
-      // exponentials, 8 columns at a time, packed and stored to the P tile at once: the row of
-      // scores is the only large array that stays in registers (no spills)
-      float rs = 0.f;
+      FA_T(3);
+      // exponentials; P goes back to TMEM as packed bf16 pairs (column c holds keys 2c, 2c+1), 32
+      // columns per store so that the first store is in flight while the second half is computed
+      float rs2[2] = {0.f, 0.f};
 #pragma unroll
-      for (int cc = 0; cc < 16; cc++) {
-        uint32_t pk4[4];
+      for (int hh = 0; hh < 2; hh++) {
+        uint32_t pr[32];
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-          const int i = cc * 8 + q * 2;
+        for (int c = 0; c < 32; c++) {
+          const int i = hh * 64 + c * 2;
           const float e0 = exp2f(fmaf(__uint_as_float(r[i]), sl2, -m_s));
           const float e1 = exp2f(fmaf(__uint_as_float(r[i + 1]), sl2, -m_s));
-          rs += e0 + e1;
+          rs2[c & 1] += e0 + e1;
           bf162 pk = __floats2bfloat162_rn(e0, e1);
-          pk4[q] = *reinterpret_cast<uint32_t*>(&pk);
+          pr[c] = *reinterpret_cast<uint32_t*>(&pk);
         }
-        *reinterpret_cast<uint4*>(sP + (cc >> 3) * C::ATOM_BYTES + sw128_off(rit, cc & 7)) =
-            make_uint4(pk4[0], pk4[1], pk4[2], pk4[3]);
+        if (C::P_TMEM) {
+          tmem_st32(tp_addr + hh * 32, pr);
+        } else {
+          // keys hh*64 .. +63 of this row are 128 bytes: one row of swizzle atom hh
+#pragma unroll
+          for (int c16 = 0; c16 < 8; c16++)
+            *reinterpret_cast<uint4*>(sP + hh * C::ATOM_BYTES + sw128_off(rit, c16)) =
+                make_uint4(pr[c16 * 4], pr[c16 * 4 + 1], pr[c16 * 4 + 2], pr[c16 * 4 + 3]);
+        }
       }
-      l_i = l_i * corr + rs;
+      if (C::P_TMEM) tmem_st_wait(); else fence_proxy_async_smem();
+      l_i = l_i * corr + (rs2[0] + rs2[1]);
       m_i = m_new;
+      FA_T(4);
       fence_before();
-      fence_proxy_async_smem();
       mbar_arrive(p_full(t));
+      FA_T(5);
+      FA_ACC(0, 0, 1); FA_ACC(1, 1, 2); FA_ACC(2, 2, 3); FA_ACC(3, 3, 4); FA_ACC(4, 4, 5);
+#ifdef LB_FA_PROFILE
+      prof[5] += 1;
+#endif
     }
+#ifdef LB_FA_PROFILE
+    if (lane == 0)
+      for (int i = 0; i < 8; i++) atomicAdd(&g_fa_prof[i], prof[i]);
+#endif
     if (ok && n_my > 0) {
       if (!mbar_wait(pv_done(t), (uint32_t)(n_my - 1) & 1u, abort_flag)) ok = false;
     }
@@ -439,7 +500,7 @@ int launch_fa_fwd(const void* q, const void* k, const void* v, FaFwdParams p, co
   p.tiles_x = (p.Sq + 255) / 256;
   const long long grid = (long long)push.n_mov + (long long)p.tiles_x * p.hq * p.B;
   if (grid > 2147483647LL) return LB_ERR_SHAPE;
-  fa_fwd_tc_kernel<D><<<(unsigned)grid, 320, C::SMEM, s>>>(tq, tk, tv, p, push);
+  fa_fwd_tc_kernel<D><<<(unsigned)grid, 384, C::SMEM, s>>>(tq, tk, tv, p, push);
   LB_CHECK_LAUNCH();
   return LB_OK;
 }
@@ -454,6 +515,15 @@ extern "C" int lb_flash_status(void* out) {
   cudaMemcpyToSymbol(g_fa_status, zeros, sizeof(zeros));
   return LB_OK;
 }
+
+#ifdef LB_FA_PROFILE
+extern "C" int lb_flash_prof(void* out) {
+  cudaMemcpyFromSymbol(out, g_fa_prof, sizeof(unsigned long long) * 16);
+  unsigned long long zeros[16] = {0};
+  cudaMemcpyToSymbol(g_fa_prof, zeros, sizeof(zeros));
+  return LB_OK;
+}
+#endif
 
 // Same contract as lb_flash_fwd (flash_attn.cu); head_dim 64 or 128, all pointers 16-byte
 // aligned, token strides multiples of 8, causal needs Sk >= Sq.  Returns LB_ERR_SHAPE otherwise.

@@ -20,6 +20,9 @@ LIB_NAME = "liblightron_b200.so"
 
 
 def lib_path() -> str:
+    override = os.environ.get("LIGHTRON_B200_LIB")           # e.g. a build with extra instrumentation
+    if override:
+        return override
     return os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc", LIB_NAME)
 
 

@@ -35,10 +35,12 @@ _ALIGN = 128
 
 
 class _Bucket:
-    __slots__ = ("start", "end", "group", "n", "shard_len", "shard_off", "pending", "n_params", "launched", "event", "seen")
+    __slots__ = ("start", "end", "group", "n", "shard_len", "shard_off", "pending", "n_params", "launched", "event", "seen",
+                 "post_scale")
 
-    def __init__(self, start, end, group, n, shard_off):
+    def __init__(self, start, end, group, n, shard_off, post_scale=1.0):
         self.start, self.end, self.group, self.n = start, end, group, n
+        self.post_scale = post_scale
         self.shard_len = (end - start) // n
         self.shard_off = shard_off
         self.pending = self.n_params = 0
@@ -130,8 +132,12 @@ class DistributedAdamW:
         # ---- buckets ----
         self.buckets: List[_Bucket] = []
         shard_off = 0
-        for (lo, hi, group, n) in ((0, dense_end, ctx.dpcp_group, n_dense),
-                                   (dense_end, flat.numel(), ctx.edpcp_group, n_expert)):
+        # An expert's autograd gradient already holds the sum over the ep source ranks whose tokens it
+        # served (the all-to-all backward brings them in), while the replica-group average below only
+        # divides by the dp/ep x cp replicas: 1/ep_size completes the mean over all data-parallel ranks.
+        ep_scale = 1.0 / max(1, int(getattr(ctx, "ep_size", 1)))
+        for (lo, hi, group, n, post) in ((0, dense_end, ctx.dpcp_group, n_dense, 1.0),
+                                         (dense_end, flat.numel(), ctx.edpcp_group, n_expert, ep_scale)):
             if hi <= lo:
                 continue
             unit = _ALIGN * n
@@ -140,7 +146,7 @@ class DistributedAdamW:
             s = lo
             while s < hi:
                 e = min(hi, s + target)
-                b = _Bucket(s, e, group, n, shard_off)
+                b = _Bucket(s, e, group, n, shard_off, post)
                 shard_off += b.shard_len
                 self.buckets.append(b)
                 s = e
@@ -230,15 +236,21 @@ class DistributedAdamW:
         if b.n == 1:
             if out.data_ptr() != g.data_ptr():
                 out.copy_(g)
+            if b.post_scale != 1.0:
+                out.mul_(b.post_scale)
             return
         if async_op and self.comm_stream is not None:
             self.comm_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.comm_stream):
                 self._reduce_scatter(g, out, b)
+                if b.post_scale != 1.0:
+                    out.mul_(b.post_scale)
                 b.event = torch.cuda.Event()
                 b.event.record(self.comm_stream)
         else:
             self._reduce_scatter(g, out, b)
+            if b.post_scale != 1.0:
+                out.mul_(b.post_scale)
 
     def _reduce_scatter(self, g, out, b: _Bucket):
         if dist.get_backend(b.group) == "gloo":

@@ -116,3 +116,56 @@ def test_ep2_moe_matches_single_process():
 
 def test_tp2_cp2_ring():
     _check(_cfg({"tp_size": 2, "cp_size": 2, "cp_mode": "ring"}), 4, 2)
+
+
+def _expert_grads(tr):
+    """Reduced gradients of the local expert parameters, read from the optimizer's gradient shard
+    (expert buckets with a single replica hold their whole arena range)."""
+    from lightron_b200.trainer import train_step_single
+    opt = tr.optimizer
+    opt.zero_grad()
+    ga = tr.cfg.training.gradient_accumulation_steps
+    for i in range(ga):
+        opt.set_requires_gradient_sync(i == ga - 1)
+        train_step_single(tr.model, next(tr.data_iter), ga, tr.device, tr.positions)
+    opt.finish_grad_sync()
+    out = {}
+    for name, p in tr.net.named_parameters():
+        if not getattr(p, "is_expert", False):
+            continue
+        b = next(b for b in opt.buckets if b.start <= p._arena_offset < b.end)
+        assert b.n == 1
+        off = b.shard_off + p._arena_offset - b.start
+        out[name] = opt.grad_shard[off:off + p.numel()].detach().clone().view(p.shape)
+    return out
+
+
+def _run_expert_grads(rank, world, raw):
+    from lightron_b200.config import parse_config
+    from lightron_b200.trainer import Trainer
+    # plain arrays: tensors sent through the result queue would travel as shared-memory handles
+    return {k: v.numpy() for k, v in _expert_grads(Trainer(parse_config(raw, env={}))).items()}
+
+
+def test_ep2_expert_gradients_match_single_process():
+    """AdamW hides a constant factor on a gradient, so the loss curves cannot see a wrong
+    normalisation of the expert gradients under expert parallelism; compare the gradients."""
+    from lightron_b200 import mesh
+    from lightron_b200.config import parse_config
+    from lightron_b200.trainer import Trainer
+    raw = _cfg({"dp_size": 2, "ep_size": 2},
+               model_kw={"moe_num_experts": 4, "moe_topk": 2, "moe_layer_freq": 2, "moe_aux_loss_coef": 0.0})
+    mesh.set_context(None)
+    single = copy.deepcopy(raw)
+    single["distributed"] = {}
+    single["training"]["gradient_accumulation_steps"] = 2
+    want = _expert_grads(Trainer(parse_config(single, env={})))
+    mesh.set_context(None)
+    got = run_distributed(_run_expert_grads, 2, raw)
+    seen = 0
+    for per_rank in got:
+        for name, g in per_rank.items():
+            w, g = want[name], torch.from_numpy(g)
+            assert torch.allclose(g, w, rtol=1e-3, atol=1e-7), f"{name}: norm ratio {float(g.norm() / w.norm()):.4f}"
+            seen += 1
+    assert seen == len(want)
