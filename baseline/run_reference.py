@@ -37,6 +37,15 @@ def _unavailable(why: str, rank: int = 0):
         print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")[:400]}), flush=True)
 
 
+LIKE_FOR_LIKE = {"llama-1.1b": "llama-1.1b-mha"}     # nearest shape the stock attention can run (no GQA)
+
+
+def _describe(e: Exception, model: str) -> str:
+    tb = traceback.extract_tb(e.__traceback__)
+    where = next((f"{os.path.relpath(f.filename, REF)}:{f.lineno}" for f in reversed(tb) if f.filename.startswith(REF)), "")
+    return f"unmodified reference raised {type(e).__name__} at {where} on {model}: {e}".replace("\n", " ")[:400]
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if not os.path.isdir(os.path.join(REF, "model")):
@@ -48,11 +57,30 @@ def run_reference(args):
     for name in ("config", "tests", "data", "model", "parallel", "layers", "utils"):
         sys.modules.pop(name, None)
     try:
-        _run(args)
-    except Exception as e:  # stock code path raised: report, do not patch
-        tb = traceback.extract_tb(e.__traceback__)
-        where = next((f"{os.path.relpath(f.filename, REF)}:{f.lineno}" for f in reversed(tb) if f.filename.startswith(REF)), "")
-        _unavailable(f"unmodified reference raised {type(e).__name__} at {where} on {args.model}: {e}", rank)
+        line = None
+        try:
+            line = _run(args, args.model)
+        except Exception as e:  # stock code path raised: report, do not patch
+            line = {"impl": "reference", "unavailable": _describe(e, args.model)}
+        # the same steps on the nearest shape the stock code runs, so that every record carries a
+        # same-box, same-shape pair next to the headline config
+        other = LIKE_FOR_LIKE.get(args.model)
+        if other is not None and not getattr(args, "no_like_for_like", False):
+            try:
+                import gc
+                import torch
+                gc.collect()
+                torch.cuda.empty_cache()
+                full = _run(args, other)
+                like = None if full is None else {"model": other, "value": full["value"], "unit": "tokens/s",
+                                                  "ms_per_step": full["ms_per_step"],
+                                                  "e2e": {"value": full["e2e"]["value"], "ms_per_step": full["e2e"]["ms_per_step"]}}
+            except Exception as e:
+                like = {"model": other, "unavailable": _describe(e, other)}
+            if line is not None and like is not None:
+                line["like_for_like"] = like
+        if rank == 0 and line is not None:
+            print(json.dumps(line), flush=True)
     finally:
         try:
             import torch.distributed as dist
@@ -62,7 +90,12 @@ def run_reference(args):
             pass
 
 
-def _run(args):
+_DIST_READY = False
+
+
+def _run(args, model_name):
+    """Builds and times one model shape; returns the JSON record on rank 0 (None elsewhere)."""
+    global _DIST_READY
     import datetime
     import statistics  # noqa: F401
     import torch
@@ -86,11 +119,13 @@ def _run(args):
     dp = n // tp
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    dist.init_process_group(backend="nccl", init_method="env://", rank=rank, world_size=n,
-                            timeout=datetime.timedelta(minutes=10))
-    setup_distributed(tp_size=tp, pp_size=1, cp_size=1, ep_size=1, dp_size=dp)
+    if not _DIST_READY:
+        dist.init_process_group(backend="nccl", init_method="env://", rank=rank, world_size=n,
+                                timeout=datetime.timedelta(minutes=10))
+        setup_distributed(tp_size=tp, pp_size=1, cp_size=1, ep_size=1, dp_size=dp)
+        _DIST_READY = True
 
-    shape = dict(SHAPES[args.model])
+    shape = dict(SHAPES[model_name])
     model_args = ModelArgs(max_seq_len=args.seq, norm_eps=1e-5, tp_size=tp, cp_size=1, moe_num_experts=1, moe_topk=2,
                            moe_layer_freq=2, **shape)
     with torch.device("meta"):
@@ -179,16 +214,18 @@ def _run(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item())
     tokens_per_step = args.mbs * dp * args.seq
+    del model, base_model, optimizer, resident
     if rank == 0:
-        print(json.dumps({
+        return ({
             "impl": "reference", "metric": METRIC, "value": tokens_per_step / (ms / 1e3), "unit": "tokens/s",
             "n_gpus": n, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (no fp32 master: stock model.to(bfloat16))",
             "data": "synthetic uniform-random token ids, random-init N(0,0.02) weights",
-            "config": {"model": args.model, "global_batch": args.mbs * dp, "seq_len": args.seq,
+            "config": {"model": model_name, "global_batch": args.mbs * dp, "seq_len": args.seq,
                        "parallelism": f"tp{tp}dp{dp}" if n > 1 else "single",
                        "l2": "working set far exceeds the 126 MB L2"},
             "clocks": clocks, "gpu_launches": 0, "final_loss": loss,
             "e2e": {"value": tokens_per_step / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 2 * args.mbs * args.seq * 8, "d2h_bytes_per_step": 4, "last_loss": lv},
-        }), flush=True)
+        })
+    return None

@@ -96,7 +96,7 @@ def save(path: str, model: nn.Module, optimizer, step: int, tokens: int, dataloa
         "rng_cpu": torch.get_rng_state(),
         "rng_cuda": torch.cuda.get_rng_state() if torch.cuda.is_available() else None,
         "data": dataloader.state_dict() if dataloader is not None else None,
-        "layout": _mesh.get_parallel_info() if ctx is _mesh.get_context() else None,
+        "layout": _layout_of(ctx),
     }
     tmp = os.path.join(opt_dir, f"rank{ctx.rank}.pt.tmp")
     torch.save(shard, tmp)
@@ -112,6 +112,23 @@ def save(path: str, model: nn.Module, optimizer, step: int, tokens: int, dataloa
         dist.barrier()
 
 
+def _layout_of(ctx) -> Dict[str, int]:
+    return {"tp": ctx.tp_size, "pp": ctx.pp_size, "cp": ctx.cp_size, "ep": ctx.ep_size, "dp": ctx.dp_size}
+
+
+def _same_layout(shard: Dict[str, Any], optimizer, ctx) -> bool:
+    """A rank's optimizer shard, RNG state and data cursor only mean something under the layout
+    that wrote them (same tp / pp / cp / ep / dp sizes, hence the same shard of the same arena)."""
+    saved = shard.get("layout")
+    if saved is not None and {k: int(v) for k, v in saved.items()} != _layout_of(ctx):
+        return False
+    opt_sd = shard.get("optimizer")
+    if opt_sd is not None and "shard_numel" in opt_sd and hasattr(optimizer, "shard_numel") \
+            and opt_sd["shard_numel"] != optimizer.shard_numel:
+        return False
+    return True
+
+
 def load(path: str, model: nn.Module, optimizer=None, dataloader=None, ctx=None) -> Dict[str, Any]:
     """Returns {'trained_steps', 'trained_tokens'}.  Raises on a corrupt / truncated file."""
     ctx = ctx or getattr(model, "ctx", None) or _mesh.get_context()
@@ -125,8 +142,14 @@ def load(path: str, model: nn.Module, optimizer=None, dataloader=None, ctx=None)
     load_full_state_dict(model, payload["model"], ctx)
     shard_file = os.path.join(path + ".opt", f"rank{ctx.rank}.pt")
     if optimizer is not None:
-        if os.path.exists(shard_file):
-            shard = torch.load(shard_file, map_location="cpu", weights_only=False)
+        shard = torch.load(shard_file, map_location="cpu", weights_only=False) if os.path.exists(shard_file) else None
+        same_layout = shard is not None and _same_layout(shard, optimizer, ctx)
+        if shard is not None and not same_layout:
+            import warnings
+            warnings.warn(f"checkpoint {path} was written with parallel layout {shard.get('layout')}, this run uses "
+                          f"{_layout_of(ctx)}: weights are re-sharded; optimizer moments, RNG state and the data "
+                          f"cursor of the old layout are not restored")
+        if same_layout:
             if shard.get("optimizer") is not None:
                 optimizer.load_state_dict(shard["optimizer"])
             if shard.get("rng_cpu") is not None:
@@ -136,6 +159,9 @@ def load(path: str, model: nn.Module, optimizer=None, dataloader=None, ctx=None)
             if dataloader is not None and shard.get("data") is not None:
                 dataloader.load_state_dict(shard["data"])
         else:
-            # different layout: weights are re-sharded, master weights restart from them
+            # different layout: weights are re-sharded, master weights restart from them, and the data
+            # cursor is recomputed from the step count (one cursor tick per micro-batch of a rank)
             optimizer.refresh_master_from_params()
+            if dataloader is not None and hasattr(dataloader, "cursor"):
+                dataloader.cursor = int(payload["trained_steps"]) * int(getattr(dataloader, "grad_acc_steps", 1))
     return {"trained_steps": payload["trained_steps"], "trained_tokens": payload["trained_tokens"]}

@@ -7,7 +7,7 @@ Parity with the reference: ``config/config.py:6-27`` (``ModelArgs`` fields and d
 
 Extensions that the reference lacks (it needs the HF hub for every run): inline model
 dimensions, explicit ``intermediate_size`` and ``rope_theta``, ``dataset.name = "synthetic"``,
-``distributed.{cp_mode, sequence_parallel, fsdp, zero}``, ``training.{dtype, save_interval,
+``distributed.{cp_mode, sequence_parallel, fsdp, fused_comm}``, ``training.{dtype, save_interval,
 resume, master_weights}``.  Both ``pp_engine`` and the sample file's ``engine`` spelling are read.
 """
 from __future__ import annotations
@@ -39,6 +39,7 @@ class ModelArgs:
     intermediate_size: Optional[int] = None   # overrides the multiple_of rule when set
     rope_theta: float = 10000.0
     moe_aux_loss_coef: float = 0.01
+    moe_capacity_factor: float = 2.0          # rows an expert-parallel rank can receive = factor x its own copies
     ep_size: int = 1
     sequence_parallel: bool = False
     cp_mode: str = "ring"                     # "ring" | "allgather" (both zig-zag causal) | "ulysses"
@@ -129,7 +130,8 @@ class DistributedConfig:
     pp_engine: str = "1f1b"
     cp_mode: str = "ring"
     sequence_parallel: bool = False
-    fsdp: bool = True            # shard params/grads/optimizer over dp (FSDP2 analogue); False = DDP + ZeRO-1
+    fsdp: bool = False           # True: parameters, gradients and optimizer state sharded per block over dp
+                                 # (parallel.fsdp engine); False: replicated bf16 parameters + sharded optimizer (ZeRO-1)
     fused_comm: bool = True      # use the peer-memory fused kernels when on CUDA
 
     @property
@@ -157,6 +159,7 @@ class TrainingConfig:
     eps: float = 1e-8
     grad_clip: float = 0.0
     jsonl_log: Optional[str] = None
+    heartbeat_timeout_s: float = 600.0   # a rank without a heartbeat for this long is reported (0 disables)
 
 
 @dataclass

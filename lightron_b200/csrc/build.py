@@ -34,19 +34,24 @@ def build(verbose: bool = False, force: bool = False) -> str:
     if not force and not needs_build():
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    objs = []
-    for src in sources():
+    objs, procs = [], []
+    for src in sources():                      # one nvcc per source, all at once
         obj = src[:-3] + ".o"
         cmd = [nvcc, *ARCH, "-O3", "-lineinfo", "-std=c++17", "--use_fast_math", "-Xcompiler", "-fPIC", "-c", src, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if verbose or r.returncode:
-            sys.stderr.write(r.stdout + r.stderr)
-        if r.returncode:
-            raise RuntimeError(f"nvcc failed on {os.path.basename(src)}")
+        procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
         objs.append(obj)
+    failed = []
+    for src, pr in procs:
+        out, err = pr.communicate()
+        if verbose or pr.returncode:
+            sys.stderr.write(out + err)
+        if pr.returncode:
+            failed.append(os.path.basename(src))
+    if failed:
+        raise RuntimeError(f"nvcc failed on {', '.join(failed)}")
     cmd = [nvcc, *ARCH, "-shared", "-o", LIB + ".tmp", *objs, "-lcudart"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode:

@@ -15,6 +15,11 @@
 #define LB_ERR_CAPACITY (-6)
 
 extern int g_lb_last_cuda_error;
+// Wall-time limit of every device-side wait on a flag that another GPU or CTA writes
+// (lb_set_flag_wait_ns; kernels take it as a launch parameter).
+extern unsigned long long g_lb_flag_wait_ns;
+// Number of SMs of the current device (queried once per device).
+int lb_num_sms();
 
 #define LB_CHECK_LAUNCH()                                   \
   do {                                                      \

@@ -13,7 +13,7 @@
 // the NVLink latency).  Two flag exchanges frame the kernel: "my gradients are complete" before any
 // peer load, and "my parameter pushes have landed" before the kernel may end, so that the next
 // forward on this stream sees every shard.  Waits are bounded and report through lb_dp_status().
-#include "common.cuh"
+#include "comm.cuh"
 
 static __device__ unsigned int g_dp_status[4] = {0, 0, 0, 0};
 
@@ -31,32 +31,19 @@ struct DpParams {
   int n, rank;
   unsigned int epoch;
   float lr, b1, b2, eps, wd, bc1, bc2, gscale;
+  unsigned long long wait_ns;      // limit of the two flag waits
 };
 
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ bool wait_ge(const unsigned int* f, unsigned int target, unsigned where) {
-  const unsigned long long t0 = globaltimer_ns();
-  while ((int)(ld_acquire_sys(f) - target) < 0) {
-    __nanosleep(100);
-    if (globaltimer_ns() - t0 > 20ull * 1000ull * 1000ull * 1000ull) {
-      atomicExch(&g_dp_status[0], 1u);
-      atomicExch(&g_dp_status[1], where);
-      return false;
-    }
-  }
-  return true;
+using lbcomm::st_release_sys;
+
+// A wait that ran out records where and makes the caller skip its share of the update: master
+// weights, moments and parameters of that block's range keep their old values, and the host sees
+// the status word at its next read (lb_dp_status), before it can checkpoint or go on training.
+__device__ __forceinline__ bool wait_ge(const unsigned int* f, unsigned int target, unsigned long long limit_ns, unsigned where) {
+  if (lbcomm::flag_wait_ge(f, target, limit_ns)) return true;
+  atomicExch(&g_dp_status[0], 1u);
+  atomicExch(&g_dp_status[1], where);
+  return false;
 }
 
 __global__ void __launch_bounds__(256) dp_adamw_kernel(const DpParams p) {
@@ -65,14 +52,18 @@ __global__ void __launch_bounds__(256) dp_adamw_kernel(const DpParams p) {
     __threadfence_system();
     st_release_sys(p.flags[threadIdx.x] + p.rank, p.epoch);
   }
-  if (threadIdx.x < p.n) wait_ge(p.flags[p.rank] + threadIdx.x, p.epoch, 1u);
+  __shared__ int s_failed;
+  if (threadIdx.x == 0) s_failed = 0;
   __syncthreads();
+  if (threadIdx.x < p.n && !wait_ge(p.flags[p.rank] + threadIdx.x, p.epoch, p.wait_ns, 1u)) s_failed = 1;
+  __syncthreads();
+  const bool failed = s_failed != 0;       // some replica's gradients never became ready: touch nothing
 
   const float inv_bc2_sqrt = rsqrtf(p.bc2);
   const float step = p.lr / p.bc1;
   const float gs = p.gscale / (float)p.n;
   const long long nvec = p.shard_len / 8;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec && !failed; i += (long long)gridDim.x * blockDim.x) {
     const long long e = p.shard_start + i * 8;
     float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int r = 0; r < p.n; r++) {
@@ -117,7 +108,7 @@ __global__ void __launch_bounds__(256) dp_adamw_kernel(const DpParams p) {
     if (threadIdx.x < p.n) {
       __threadfence_system();
       st_release_sys(p.flags[threadIdx.x] + 8 + p.rank, p.epoch);
-      wait_ge(p.flags[p.rank] + 8 + threadIdx.x, p.epoch, 2u);
+      wait_ge(p.flags[p.rank] + 8 + threadIdx.x, p.epoch, p.wait_ns, 2u);
     }
   }
 }
@@ -150,6 +141,7 @@ extern "C" int lb_dp_adamw(void* const* grad_ptrs, void* const* param_ptrs, void
   p.block_counter = (unsigned int*)block_counter;
   p.master = (float*)master; p.m = (float*)m; p.v = (float*)v;
   p.shard_start = shard_start; p.shard_len = shard_len; p.n = n; p.rank = rank; p.epoch = epoch;
+  p.wait_ns = g_lb_flag_wait_ns;
   p.lr = lr; p.b1 = b1; p.b2 = b2; p.eps = eps; p.wd = wd; p.bc1 = bc1; p.bc2 = bc2; p.gscale = gscale;
   dp_adamw_kernel<<<grid_blocks, 256, 0, (cudaStream_t)stream>>>(p);
   LB_CHECK_LAUNCH();

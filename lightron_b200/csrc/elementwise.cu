@@ -4,9 +4,33 @@
 // lengths and strides must be multiples of 8 elements.
 #include "common.cuh"
 
+#include <mutex>
+
 int g_lb_last_cuda_error = 0;
+unsigned long long g_lb_flag_wait_ns = 20ull * 1000ull * 1000ull * 1000ull;
 
 extern "C" int lb_last_error() { return g_lb_last_cuda_error; }
+
+// Wall-time limit (ns) after which a kernel stops waiting for a flag of a peer GPU and reports
+// through its status word.  Applies to launches made after the call.
+extern "C" int lb_set_flag_wait_ns(unsigned long long ns) {
+  if (ns == 0) return LB_ERR_ARG;
+  g_lb_flag_wait_ns = ns;
+  return LB_OK;
+}
+
+int lb_num_sms() {
+  static int sms[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (sms[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    sms[dev] = n;
+  }
+  return sms[dev];
+}
+extern "C" int lb_sm_count() { return lb_num_sms(); }
 
 // ---------------------------------------------------------------------------------------
 // RMSNorm.  One warp per row, two passes over the row (the second hits L1/L2).
@@ -62,7 +86,7 @@ extern "C" int lb_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
                               int cols, float eps, void* stream) {
   if (cols % 8 || rows <= 0) return LB_ERR_SHAPE;
   int blocks = (rows + 7) / 8;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > lb_num_sms() * 8) blocks = lb_num_sms() * 8;
   cudaStream_t s = (cudaStream_t)stream;
   if (res)
     rmsnorm_fwd_kernel<true><<<blocks, 256, 0, s>>>((const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)h,
@@ -268,7 +292,7 @@ extern "C" int lb_rmsnorm_bwd_blocks(int rows, int cols) {
   const bool blk = vpt <= 4 && nvec % vpt == 0 && (nvec / vpt) % 32 == 0;
   const int per_sm = !blk ? 2 : (vpt == 1 ? 3 : (vpt <= 3 ? 2 : 1));
   int blocks = (rows + 7) / 8;
-  if (blocks > 148 * per_sm) blocks = 148 * per_sm;
+  if (blocks > lb_num_sms() * per_sm) blocks = lb_num_sms() * per_sm;
   return blocks < 1 ? 1 : blocks;
 }
 
@@ -327,7 +351,7 @@ extern "C" int lb_rope(void* t, const void* cosT, const void* sinT, const void* 
   if (head_dim % 8 || ld % 8 || tokens <= 0) return LB_ERR_SHAPE;
   long long total = (long long)tokens * n_heads * (head_dim / 8);
   int blocks = (int)((total + 255) / 256);
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > lb_num_sms() * 16) blocks = lb_num_sms() * 16;
   rope_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((bf16*)t, (const float*)cosT, (const float*)sinT,
                                                         (const int*)positions, tokens, S, n_heads, head_dim, ld,
                                                         inverse);
@@ -338,7 +362,9 @@ extern "C" int lb_rope(void* t, const void* cosT, const void* sinT, const void* 
 // ---------------------------------------------------------------------------------------
 // SwiGLU on a fused [rows, 2I] gate|up matrix (row stride ld).
 // ---------------------------------------------------------------------------------------
-__global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int rows, int I, long long ld) {
+__global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int rows, int I, long long ld,
+                                  const int* __restrict__ rows_dev) {
+  if (rows_dev) rows = max(0, min(rows, *rows_dev));     // row count known only on the device (MoE segments)
   const int vec = I >> 3;
   const long long total = (long long)rows * vec;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -355,7 +381,8 @@ __global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict_
 }
 
 __global__ void swiglu_bwd_kernel(const bf16* __restrict__ gu, const bf16* __restrict__ dy, bf16* __restrict__ dgu,
-                                  int rows, int I, long long ld) {
+                                  int rows, int I, long long ld, const int* __restrict__ rows_dev) {
+  if (rows_dev) rows = max(0, min(rows, *rows_dev));
   const int vec = I >> 3;
   const long long total = (long long)rows * vec;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -379,24 +406,32 @@ __global__ void swiglu_bwd_kernel(const bf16* __restrict__ gu, const bf16* __res
 
 static inline int ew_blocks(long long total) {
   long long b = (total + 255) / 256;
-  if (b > 148 * 16) b = 148 * 16;
+  if (b > lb_num_sms() * 16) b = lb_num_sms() * 16;
   return (int)(b < 1 ? 1 : b);
 }
 
-extern "C" int lb_swiglu_fwd(const void* gu, void* out, int rows, int I, long long ld, void* stream) {
+// rows_dev (or null): device int; only the first min(rows, *rows_dev) rows are processed.
+extern "C" int lb_swiglu_fwd_dev(const void* gu, void* out, int rows, int I, long long ld, const void* rows_dev, void* stream) {
   if (I % 8 || ld % 8 || rows <= 0) return LB_ERR_SHAPE;
   swiglu_fwd_kernel<<<ew_blocks((long long)rows * (I / 8)), 256, 0, (cudaStream_t)stream>>>((const bf16*)gu, (bf16*)out,
-                                                                                            rows, I, ld);
+                                                                                            rows, I, ld, (const int*)rows_dev);
   LB_CHECK_LAUNCH();
   return LB_OK;
 }
+extern "C" int lb_swiglu_fwd(const void* gu, void* out, int rows, int I, long long ld, void* stream) {
+  return lb_swiglu_fwd_dev(gu, out, rows, I, ld, nullptr, stream);
+}
 
-extern "C" int lb_swiglu_bwd(const void* gu, const void* dy, void* dgu, int rows, int I, long long ld, void* stream) {
+extern "C" int lb_swiglu_bwd_dev(const void* gu, const void* dy, void* dgu, int rows, int I, long long ld,
+                                 const void* rows_dev, void* stream) {
   if (I % 8 || ld % 8 || rows <= 0) return LB_ERR_SHAPE;
   swiglu_bwd_kernel<<<ew_blocks((long long)rows * (I / 8)), 256, 0, (cudaStream_t)stream>>>(
-      (const bf16*)gu, (const bf16*)dy, (bf16*)dgu, rows, I, ld);
+      (const bf16*)gu, (const bf16*)dy, (bf16*)dgu, rows, I, ld, (const int*)rows_dev);
   LB_CHECK_LAUNCH();
   return LB_OK;
+}
+extern "C" int lb_swiglu_bwd(const void* gu, const void* dy, void* dgu, int rows, int I, long long ld, void* stream) {
+  return lb_swiglu_bwd_dev(gu, dy, dgu, rows, I, ld, nullptr, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -437,7 +472,7 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ tok, const bf
 extern "C" int lb_embedding_fwd(const void* tok, const void* w, void* out, int T, int H, int v0, int v1, void* stream) {
   if (H % 8 || T <= 0) return LB_ERR_SHAPE;
   int blocks = (T + 7) / 8;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > lb_num_sms() * 8) blocks = lb_num_sms() * 8;
   embedding_fwd_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const long long*)tok, (const bf16*)w, (bf16*)out, T,
                                                                  H, v0, v1);
   LB_CHECK_LAUNCH();
@@ -447,7 +482,7 @@ extern "C" int lb_embedding_fwd(const void* tok, const void* w, void* out, int T
 extern "C" int lb_embedding_bwd(const void* tok, const void* dy, void* dw, int T, int H, int v0, int v1, void* stream) {
   if (H % 8 || T <= 0) return LB_ERR_SHAPE;
   int blocks = (T + 7) / 8;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > lb_num_sms() * 8) blocks = lb_num_sms() * 8;
   embedding_bwd_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const long long*)tok, (const bf16*)dy, (bf16*)dw, T,
                                                                  H, v0, v1);
   LB_CHECK_LAUNCH();
@@ -673,6 +708,10 @@ extern "C" int lb_add_inplace(void* a, const void* b, long long n, void* stream)
 //    different threads) write the same rows and race: serialise them.
 //  * Inputs, outputs and results are those of lb_rmsnorm_bwd; only the summation order over
 //    blocks may differ (fewer, larger blocks), which changes dw by fp32 rounding only.
+//  * It always runs the general kernel (row per warp, dw partial sums through shared-memory
+//    atomics), not the faster block-per-row kernel that lb_rmsnorm_bwd picks for common widths:
+//    that one needs one scratch row per resident block, up to 444 rows, which would not fit the
+//    128 rows of the fixed array.  Expect roughly 1.5x the run time of lb_rmsnorm_bwd.
 // ---------------------------------------------------------------------------------------
 #define LB_STATIC_SCRATCH_MAX_COLS 8192
 #define LB_STATIC_SCRATCH_MAX_BLOCKS 128
@@ -680,6 +719,7 @@ static __device__ __align__(256) float g_rmsnorm_static_scratch[LB_STATIC_SCRATC
 
 #define LB_MAX_DEVICES 64
 static float* g_static_scratch_addr[LB_MAX_DEVICES] = {nullptr};
+static std::mutex g_static_scratch_mutex;     // the per-device address table is filled under this lock
 
 extern "C" int lb_rmsnorm_bwd_static(const void* dy, const void* x, const void* w, const void* rstd, const void* dres,
                                      void* dx, void* dw, int rows, int cols, void* stream) {
@@ -688,14 +728,18 @@ extern "C" int lb_rmsnorm_bwd_static(const void* dy, const void* x, const void* 
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= LB_MAX_DEVICES) { g_lb_last_cuda_error = (int)e; return LB_ERR_ARG; }
-  if (g_static_scratch_addr[dev] == nullptr) {
-    // In host code the array's name is only a handle; the kernel needs its device address.
-    float* p = nullptr;
-    e = cudaGetSymbolAddress((void**)&p, g_rmsnorm_static_scratch);
-    if (e != cudaSuccess || p == nullptr) { g_lb_last_cuda_error = (int)e; return LB_ERR_LAUNCH; }
-    g_static_scratch_addr[dev] = p;
+  float* partial = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_addr[dev] == nullptr) {
+      // In host code the array's name is only a handle; the kernel needs its device address.
+      float* p = nullptr;
+      e = cudaGetSymbolAddress((void**)&p, g_rmsnorm_static_scratch);
+      if (e != cudaSuccess || p == nullptr) { g_lb_last_cuda_error = (int)e; return LB_ERR_LAUNCH; }
+      g_static_scratch_addr[dev] = p;
+    }
+    partial = g_static_scratch_addr[dev];
   }
-  float* partial = g_static_scratch_addr[dev];
   int nblk = lb_rmsnorm_bwd_blocks(rows, cols);
   if (nblk > LB_STATIC_SCRATCH_MAX_BLOCKS) nblk = LB_STATIC_SCRATCH_MAX_BLOCKS;
   cudaStream_t s = (cudaStream_t)stream;

@@ -588,14 +588,14 @@ int launch_bwd(const BwdParams& p, cudaStream_t s) {
     attr = true;
   }
   const long long rows = (long long)p.B * p.Sq * p.hq;
-  int dblocks = (int)((rows + 7) / 8 > 148 * 8 ? 148 * 8 : (rows + 7) / 8);
+  int dblocks = (int)((rows + 7) / 8 > lb_num_sms() * 8 ? lb_num_sms() * 8 : (rows + 7) / 8);
   flash_delta_kernel<D><<<dblocks, 256, 0, s>>>(p);
   LB_CHECK_LAUNCH();
   dim3 grid((p.Sk + 63) / 64, p.hkv, p.B);
   flash_bwd_kernel<D><<<grid, 128, smem, s>>>(p);
   LB_CHECK_LAUNCH();
   const long long total = rows * (D / 8);
-  int cblocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+  int cblocks = (int)((total + 255) / 256 > lb_num_sms() * 16 ? lb_num_sms() * 16 : (total + 255) / 256);
   flash_dq_convert_kernel<D><<<cblocks, 256, 0, s>>>(p);
   LB_CHECK_LAUNCH();
   return LB_OK;

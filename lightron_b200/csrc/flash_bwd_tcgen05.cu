@@ -487,14 +487,14 @@ int launch_fa_bwd(const void* q, const void* k, const void* v, const FaBwdParams
   }
   const long long rows = (long long)p.B * p.Sq * p.hq;
   const long long rows_per_block = 256 / (D / 8);
-  int dblocks = (int)((rows + rows_per_block - 1) / rows_per_block > 148 * 16 ? 148 * 16 : (rows + rows_per_block - 1) / rows_per_block);
+  int dblocks = (int)((rows + rows_per_block - 1) / rows_per_block > lb_num_sms() * 16 ? lb_num_sms() * 16 : (rows + rows_per_block - 1) / rows_per_block);
   fa_delta_kernel<D><<<dblocks, 256, 0, s>>>(p);
   LB_CHECK_LAUNCH();
   dim3 grid((p.Sk + 127) / 128, p.hkv, p.B);
   fa_bwd_tc_kernel<D><<<grid, C::NTHREADS, C::SMEM, s>>>(tq, tk, tv, tdo, p);
   LB_CHECK_LAUNCH();
   const long long total = rows * (D / 8);
-  int cblocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+  int cblocks = (int)((total + 255) / 256 > lb_num_sms() * 16 ? lb_num_sms() * 16 : (total + 255) / 256);
   fa_dq_convert_kernel<D><<<cblocks, 256, 0, s>>>(p);
   LB_CHECK_LAUNCH();
   return LB_OK;

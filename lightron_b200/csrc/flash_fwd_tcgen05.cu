@@ -21,6 +21,7 @@
 // All waits are bounded; on expiry a status word is set and the CTA drains and frees its TMEM.
 #include <string.h>
 #include "tcgen05.cuh"
+#include "comm.cuh"
 
 static __device__ unsigned int g_fa_status[4] = {0, 0, 0, 0};
 
@@ -64,28 +65,8 @@ struct FaFwdParams {
   const unsigned int* kv_flags;  // null, or this rank's block counters [B][kv_brows / 128]
   unsigned int flag_target;
   int tiles_x;                   // query tiles (256 rows) per (batch, head)
+  unsigned long long wait_ns;    // limit of a wait on a key block's arrival flag
 };
-
-__device__ __forceinline__ unsigned int fa_ld_acquire_sys(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ unsigned long long fa_globaltimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// bounded (~20 s) wait for a peer's pushes
-__device__ __forceinline__ bool fa_flag_wait(const unsigned int* f, unsigned int target) {
-  if ((int)(fa_ld_acquire_sys(f) - target) >= 0) return true;
-  const unsigned long long t0 = fa_globaltimer();
-  while ((int)(fa_ld_acquire_sys(f) - target) < 0) {
-    __nanosleep(100);
-    if (fa_globaltimer() - t0 > 20ull * 1000ull * 1000ull * 1000ull) return false;
-  }
-  return true;
-}
 
 template <int D>
 struct FaCfg {
@@ -152,7 +133,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       __threadfence_system();
       __syncwarp();
       if (lane == 0)
-        asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(push.flags[dst] + (grow0 >> 7)), "r"(1u) : "memory");
+        lbcomm::red_release_sys_add(push.flags[dst] + (grow0 >> 7), 1u);
     }
     return;
   }
@@ -229,7 +210,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         if (p.kv_flags) {
           // this 128-key block is pushed by its owner: wait for its counter, then order the
           // peer's generic-proxy writes before the TMA (async proxy) reads
-          if (!fa_flag_wait(p.kv_flags + (long long)b * (p.kv_brows >> 7) + j, p.flag_target)) { *abort_flag = 1; ok = false; break; }
+          if (!lbcomm::flag_wait_ge(p.kv_flags + (long long)b * (p.kv_brows >> 7) + j, p.flag_target, p.wait_ns)) { *abort_flag = 1; ok = false; break; }
           asm volatile("fence.proxy.async;" ::: "memory");
         }
         mbar_expect_tx(k_full(ks), C::TILE_BYTES);
@@ -498,6 +479,7 @@ int launch_fa_fwd(const void* q, const void* k, const void* v, FaFwdParams p, co
     attr = true;
   }
   p.tiles_x = (p.Sq + 255) / 256;
+  p.wait_ns = g_lb_flag_wait_ns;
   const long long grid = (long long)push.n_mov + (long long)p.tiles_x * p.hq * p.B;
   if (grid > 2147483647LL) return LB_ERR_SHAPE;
   fa_fwd_tc_kernel<D><<<(unsigned)grid, 384, C::SMEM, s>>>(tq, tk, tv, p, push);

@@ -24,6 +24,7 @@
 #include <vector>
 #include "common.cuh"
 #include "tcgen05.cuh"
+#include "comm.cuh"
 
 static __device__ unsigned int g_grp_status[4] = {0, 0, 0, 0};
 
@@ -78,14 +79,14 @@ __device__ __forceinline__ void give_up(volatile int* abort_flag, unsigned where
 template <bool A_MN, bool B_MN>
 __device__ __forceinline__ bool produce_tile(const CUtensorMap* ta, const CUtensorMap* tb, int m0, int n0, int num_kb,
                                              uint32_t smem_base, uint32_t bar_base, int& stage, uint32_t& phase,
-                                             volatile int* abort_flag) {
+                                             volatile int* abort_flag, int k_base = 0) {
   for (int kb = 0; kb < num_kb; kb++) {
     if (!bw::mbar_wait(bar_base + 8u * (STAGES + stage), phase ^ 1u, abort_flag)) return false;
     const uint32_t fb = bar_base + 8u * stage;
     bw::mbar_expect_tx(fb, STAGE_BYTES);
     const uint32_t sa = smem_base + stage * STAGE_BYTES;
     const uint32_t sb = sa + A_BYTES;
-    const int k0 = kb * BK;
+    const int k0 = k_base + kb * BK;
     if (!A_MN) {
       bw::tma_load_2d(sa, ta, k0, m0, fb);                                                      // box {64 k, 128 m}
     } else {
@@ -279,13 +280,233 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_grouped_kernel(const __gr
   }
 }
 
+// ---- ragged variant: row segments whose sizes live in device memory --------------------------------
+// The per-expert GEMMs of a MoE layer.  One activation buffer [cap, K] holds the rows of all local
+// experts, expert e in rows [seg[e], seg[e] + seg[LE + e]); every segment starts on a multiple of
+// 128 rows and the rows between a segment's end and the next multiple of 128 are zero.  Offsets and
+// counts are written by the planning kernel of the token exchange (moe.cu) and are never read on
+// the host: every role of every CTA derives the same tile list from them.
+//   mode 0   C[rows of e, N] = A[rows of e, K] . op(B_e)^T           (forward, data gradient)
+//            all tiles cost the same, so CTA c simply takes tiles c, c + grid, ...
+//   mode 1   C_e[Nw, Kw] (+)= A[rows of e, Nw]^T . B[rows of e, Kw]  (weight gradient; the reduction
+//            runs over the rows of the segment, in 64-row steps, padding rows contribute zeros)
+// Before its first load the producer can wait (bounded) for an arrival word: the rows are pushed
+// into A by other GPUs.
+struct RaggedParams {
+  CUtensorMap ta;                      // mode 0: [cap, K] K-major;  mode 1: [cap, Nw] as MN-major A
+  CUtensorMap tb[MAX_PROBLEMS];        // mode 0: B_e;               mode 1: tb[0] = [cap, Kw] as MN-major B
+  bf16* C[MAX_PROBLEMS];               // mode 0: C[0] = common [cap, N];  mode 1: C_e
+  long long ldc;
+  const int* seg;
+  int LE, M_w, N, K, b_mn, mode, accumulate, cap;
+  int tiles_n, tiles_m_w, num_kb;
+  const unsigned int* wait_flag;
+  unsigned int wait_target;
+  unsigned long long wait_ns;
+};
+
+struct RaggedTile { int e, m0, n0, num_kb, k_base; };
+
+// Tile `t` of the launch, or e < 0 past the end.  seg_* are the CTA's shared copies of the table.
+__device__ __forceinline__ RaggedTile ragged_tile(int t, const RaggedParams& rp, const int* s_off, const int* s_tiles) {
+  RaggedTile r;
+  r.e = -1; r.m0 = r.n0 = r.num_kb = r.k_base = 0;
+  if (rp.mode == 0) {
+    for (int e = 0; e < rp.LE; e++) {
+      const int nt = s_tiles[e] * rp.tiles_n;
+      if (t < nt) {
+        Problem pr;
+        pr.tiles_m = s_tiles[e]; pr.tiles_n = rp.tiles_n;
+        int tm, tn;
+        tile_coords(t, pr, tm, tn);
+        r.e = e; r.m0 = s_off[e] + tm * BM; r.n0 = tn * BN; r.num_kb = rp.num_kb;
+        return r;
+      }
+      t -= nt;
+    }
+  } else {
+    const int per = rp.tiles_m_w * rp.tiles_n;
+    const int e = t / per;
+    if (e < rp.LE) {
+      const int tt = t - e * per;
+      r.e = e; r.m0 = (tt % rp.tiles_m_w) * BM; r.n0 = (tt / rp.tiles_m_w) * BN;
+      r.num_kb = s_tiles[e];              // 64-row steps over the segment
+      r.k_base = s_off[e];
+    }
+  }
+  return r;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_ragged_kernel(const __grid_constant__ RaggedParams rp) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  __shared__ int s_abort;
+  __shared__ int s_off[MAX_PROBLEMS], s_tiles[MAX_PROBLEMS];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = bw::smem_u32(smem);
+  const uint32_t bar_base = bw::smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES; s++) {
+      bw::mbar_init(full_bar(s), 1);
+      bw::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; a++) {
+      bw::mbar_init(tfull_bar(a), 1);
+      bw::mbar_init(tempty_bar(a), 4);
+    }
+    bw::mbar_init_fence();
+  }
+  if (threadIdx.x < rp.LE) {
+    // segment table -> offsets and tile (mode 0: 128-row tiles) / step (mode 1: 64-row steps) counts,
+    // clamped so that no coordinate can pass the end of the buffer
+    int off = rp.seg[threadIdx.x], cnt = rp.seg[rp.LE + threadIdx.x];
+    if (off < 0 || off > rp.cap) { off = 0; cnt = 0; }
+    if (cnt < 0) cnt = 0;
+    if (off + cnt > rp.cap) cnt = rp.cap - off;
+    s_off[threadIdx.x] = off;
+    s_tiles[threadIdx.x] = rp.mode == 0 ? (cnt + BM - 1) / BM : (cnt + BK - 1) / BK;
+  }
+  if (warp == 1) bw::tmem_alloc(bw::smem_u32(tmem_slot), 512);
+  bw::fence_before();
+  __syncthreads();
+  bw::fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      if (rp.wait_flag) {
+        // the rows of A are pushed by other GPUs: acquire the arrival word, then order their
+        // generic-proxy writes before the TMA (async proxy) reads
+        if (!lbcomm::flag_wait_ge(rp.wait_flag, rp.wait_target, rp.wait_ns)) { give_up(abort_flag, 11u); ok = false; }
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
+      for (int t = blockIdx.x; ok; t += gridDim.x) {
+        const RaggedTile rt = ragged_tile(t, rp, s_off, s_tiles);
+        if (rt.e < 0) break;
+        if (rt.num_kb == 0) continue;
+        if (rp.mode == 0) {
+          if (!rp.b_mn) ok = produce_tile<false, false>(&rp.ta, &rp.tb[rt.e], rt.m0, rt.n0, rt.num_kb, smem_base, bar_base, stage, phase, abort_flag);
+          else          ok = produce_tile<false, true>(&rp.ta, &rp.tb[rt.e], rt.m0, rt.n0, rt.num_kb, smem_base, bar_base, stage, phase, abort_flag);
+        } else {
+          ok = produce_tile<true, true>(&rp.ta, &rp.tb[0], rt.m0, rt.n0, rt.num_kb, smem_base, bar_base, stage, phase, abort_flag, rt.k_base);
+        }
+        if (!ok) give_up(abort_flag, 1u);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int n = 0;
+      for (int t = blockIdx.x; ok; t += gridDim.x) {
+        const RaggedTile rt = ragged_tile(t, rp, s_off, s_tiles);
+        if (rt.e < 0) break;
+        if (rt.num_kb == 0) continue;
+        const int acc = n & 1;
+        const uint32_t acc_phase = (uint32_t)(n >> 1) & 1u;
+        if (!bw::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { give_up(abort_flag, 2u); ok = false; break; }
+        bw::fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
+        if (rp.mode == 0) {
+          if (!rp.b_mn) ok = mma_tile<false, false>(d_tmem, rt.num_kb, smem_base, bar_base, stage, phase, abort_flag);
+          else          ok = mma_tile<false, true>(d_tmem, rt.num_kb, smem_base, bar_base, stage, phase, abort_flag);
+        } else {
+          ok = mma_tile<true, true>(d_tmem, rt.num_kb, smem_base, bar_base, stage, phase, abort_flag);
+        }
+        if (ok) bw::umma_commit(tfull_bar(acc));
+        else give_up(abort_flag, 3u);
+        n++;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (4 warps) ------------------------------
+    const int quad = warp & 3;
+    int n = 0;
+    for (int t = blockIdx.x;; t += gridDim.x) {
+      const RaggedTile rt = ragged_tile(t, rp, s_off, s_tiles);
+      if (rt.e < 0) break;
+      if (rt.num_kb == 0) continue;
+      const int acc = n & 1;
+      const uint32_t acc_phase = (uint32_t)(n >> 1) & 1u;
+      if (!bw::mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { give_up(abort_flag, 4u); break; }
+      bw::fence_after();
+      const int row = rt.m0 + quad * 32 + lane;
+      const int row_end = rp.mode == 0 ? rp.cap : rp.M_w;      // mode 0 writes whole 128-row tiles (padding rows are zeros)
+      bf16* const pC = rp.mode == 0 ? rp.C[0] : rp.C[rt.e];
+      const bool accumulate = rp.accumulate != 0;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * BN;
+      bf16* crow = pC + (size_t)row * rp.ldc + rt.n0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c++) {
+        uint32_t r[32];
+        bw::tmem_ld32(taddr + c * 32, r);
+        bw::tmem_ld_wait();
+        if (row < row_end) {
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            const int col = rt.n0 + c * 32 + g * 8;
+            if (col < rp.N) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[g * 8 + i]);
+              uint4* dst = reinterpret_cast<uint4*>(crow + c * 32 + g * 8);
+              if (accumulate) {
+                float o[8];
+                unpack8(*dst, o);
+#pragma unroll
+                for (int i = 0; i < 8; i++) f[i] += o[i];
+              }
+              *dst = pack8(f);
+            }
+          }
+        }
+      }
+      bw::fence_before();
+      __syncwarp();
+      if (lane == 0) bw::mbar_arrive(tempty_bar(acc));
+      n++;
+    }
+  }
+
+  bw::fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    bw::fence_after();
+    bw::tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // ---- host side: static schedule, cached per (device, shapes) -------------------------------------
 struct Schedule {
   int grid = 0;
   int* d_offsets = nullptr;
   int* d_items = nullptr;
+  unsigned long long last_use = 0;
 };
+// Cache of uploaded schedules, keyed by (device, M, N, K of every problem).  A training run uses a
+// few dozen shape sets; callers whose row counts change from call to call (expert-parallel MoE)
+// use lb_gemm_ragged instead, which takes the counts from device memory and needs no schedule.
+// The cache is still bounded: beyond MAX_SCHEDULES entries the least recently used one is freed.
+constexpr size_t MAX_SCHEDULES = 128;
 std::map<std::vector<int>, Schedule> g_schedules;
+unsigned long long g_sched_clock = 0;
 std::mutex g_sched_mutex;
 int g_sms = 0;
 
@@ -366,6 +587,12 @@ extern "C" int lb_gemm_grouped_status(void* out) {
 // Host only (no CUDA call): the schedule lb_gemm_grouped would build for these shapes on `sms` SMs.
 // out[0] = load of the busiest CTA, out[1] = total work, out[2] = number of CTAs used, all in k-block
 // units of 64 (a tile counts its k-blocks + 6).  busiest * CTAs / total is the imbalance factor.
+// Number of schedules currently cached (never more than MAX_SCHEDULES).
+extern "C" int lb_gemm_grouped_cached() {
+  std::lock_guard<std::mutex> lock(g_sched_mutex);
+  return (int)g_schedules.size();
+}
+
 extern "C" int lb_gemm_grouped_plan(int n, const int* M, const int* N, const int* K, int sms, long long* out) {
   if (n < 1 || n > MAX_PROBLEMS || sms < 1) return LB_ERR_SHAPE;
   Problem probs[MAX_PROBLEMS];
@@ -425,16 +652,92 @@ extern "C" int lb_gemm_grouped(int n, const void* const* A, const void* const* B
     std::lock_guard<std::mutex> lock(g_sched_mutex);
     auto it = g_schedules.find(key);
     if (it == g_schedules.end()) {
+      if (g_schedules.size() >= MAX_SCHEDULES) {
+        // evict the least recently used entry; cudaFree waits for kernels that may still read it
+        auto victim = g_schedules.begin();
+        for (auto j = g_schedules.begin(); j != g_schedules.end(); ++j)
+          if (j->second.last_use < victim->second.last_use) victim = j;
+        cudaFree(victim->second.d_offsets);
+        cudaFree(victim->second.d_items);
+        g_schedules.erase(victim);
+      }
       Schedule s;
       int rc = build_schedule(gp.prob, n, g_sms, &s);
       if (rc) return rc;
       it = g_schedules.emplace(key, s).first;
     }
+    it->second.last_use = ++g_sched_clock;
     sched = it->second;
   }
   gp.offsets = sched.d_offsets;
   gp.items = sched.d_items;
   gemm_grouped_kernel<<<sched.grid, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(gp);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}
+
+
+// Expert GEMMs over ragged row segments (see gemm_ragged_kernel).  seg: device table of 2 * LE + 2
+// ints (offsets, counts, ...), LE <= 8 local experts.
+//  mode 0: C [cap, N] = A [cap, K] . op(B_e)^T per segment; B: host array of LE weight pointers
+//          ([N, K], or [K, N] with b_mn), all with leading dimension ldb.  wait_flag (or null): device
+//          word that must reach wait_target before A is read.
+extern "C" int lb_gemm_ragged(const void* A, const void* const* B, void* C, const void* seg, int LE, int cap, int N, int K,
+                              long long lda, long long ldb, long long ldc, int b_mn, const void* wait_flag,
+                              unsigned int wait_target, void* stream) {
+  if (LE < 1 || LE > MAX_PROBLEMS || cap <= 0 || N <= 0 || K <= 0) return LB_ERR_SHAPE;
+  if ((lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8) || (K % 8)) return LB_ERR_SHAPE;
+  if (((uintptr_t)A | (uintptr_t)C) & 15) return LB_ERR_ARG;
+  static thread_local RaggedParams rp;
+  int rc = bw::make_map_bf16(&rp.ta, A, (uint64_t)K, (uint64_t)cap, (uint64_t)lda, BK, BM);
+  if (rc) return rc;
+  for (int e = 0; e < LE; e++) {
+    if ((uintptr_t)B[e] & 15) return LB_ERR_ARG;
+    if (!b_mn) rc = bw::make_map_bf16(&rp.tb[e], B[e], (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, BN);
+    else       rc = bw::make_map_bf16(&rp.tb[e], B[e], (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK);
+    if (rc) return rc;
+    rp.C[e] = nullptr;
+  }
+  rp.C[0] = (bf16*)C; rp.ldc = ldc; rp.seg = (const int*)seg; rp.LE = LE; rp.M_w = 0; rp.N = N; rp.K = K; rp.b_mn = b_mn;
+  rp.mode = 0; rp.accumulate = 0; rp.cap = cap;
+  rp.tiles_n = (N + BN - 1) / BN; rp.tiles_m_w = 0; rp.num_kb = (K + BK - 1) / BK;
+  rp.wait_flag = (const unsigned int*)wait_flag; rp.wait_target = wait_target; rp.wait_ns = g_lb_flag_wait_ns;
+  {
+    std::lock_guard<std::mutex> lock(g_sched_mutex);
+    static bool attr = false;
+    if (!attr) { cudaFuncSetAttribute(gemm_ragged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); attr = true; }
+  }
+  gemm_ragged_kernel<<<lb_num_sms(), NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(rp);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}
+
+//  Weight gradients: C_e [Nw, Kw] (+)= dY[rows of e, Nw]^T . X[rows of e, Kw]; C: host array of LE
+//  gradient pointers with leading dimension ldc.
+extern "C" int lb_gemm_ragged_wgrad(const void* dY, const void* X, void* const* C, const void* seg, int LE, int cap, int Nw,
+                                    int Kw, long long lddy, long long ldx, long long ldc, int accumulate, void* stream) {
+  if (LE < 1 || LE > MAX_PROBLEMS || cap <= 0 || Nw <= 0 || Kw <= 0) return LB_ERR_SHAPE;
+  if ((lddy % 8) || (ldx % 8) || (ldc % 8) || (Nw % 8) || (Kw % 8)) return LB_ERR_SHAPE;
+  if (((uintptr_t)dY | (uintptr_t)X) & 15) return LB_ERR_ARG;
+  static thread_local RaggedParams rp;
+  int rc = bw::make_map_bf16(&rp.ta, dY, (uint64_t)Nw, (uint64_t)cap, (uint64_t)lddy, 64, BK);
+  if (rc) return rc;
+  rc = bw::make_map_bf16(&rp.tb[0], X, (uint64_t)Kw, (uint64_t)cap, (uint64_t)ldx, 64, BK);
+  if (rc) return rc;
+  for (int e = 0; e < LE; e++) {
+    if ((uintptr_t)C[e] & 15) return LB_ERR_ARG;
+    rp.C[e] = (bf16*)C[e];
+  }
+  rp.ldc = ldc; rp.seg = (const int*)seg; rp.LE = LE; rp.M_w = Nw; rp.N = Kw; rp.K = 0; rp.b_mn = 1; rp.mode = 1;
+  rp.accumulate = accumulate; rp.cap = cap;
+  rp.tiles_n = (Kw + BN - 1) / BN; rp.tiles_m_w = (Nw + BM - 1) / BM; rp.num_kb = 0;
+  rp.wait_flag = nullptr; rp.wait_target = 0; rp.wait_ns = g_lb_flag_wait_ns;
+  {
+    std::lock_guard<std::mutex> lock(g_sched_mutex);
+    static bool attr = false;
+    if (!attr) { cudaFuncSetAttribute(gemm_ragged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); attr = true; }
+  }
+  gemm_ragged_kernel<<<lb_num_sms(), NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(rp);
   LB_CHECK_LAUNCH();
   return LB_OK;
 }

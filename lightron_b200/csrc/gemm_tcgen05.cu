@@ -19,6 +19,8 @@
 #include <cuda.h>
 #include <string.h>
 #include "common.cuh"
+#include "tcgen05.cuh"
+#include "comm.cuh"
 
 // Device-side status words of the GEMM kernels.  A bounded wait that runs out sets word 0 to a
 // non-zero code and word 1 to a location id instead of spinning forever; the host reads them
@@ -35,97 +37,20 @@ constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int NUM_THREADS = 192;
-constexpr uint32_t WAIT_LIMIT = 1u << 20;
 constexpr int GROUP_M = 8;
 
-// ---- PTX wrappers -------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// The PTX wrappers (mbarrier, TMA, tcgen05, descriptors, tensor maps) live in tcgen05.cuh, the
+// flag primitives in comm.cuh.
+using namespace bw;
 
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false (and records where) when the limit is hit or another role has
-// already given up.
+// Bounded mbarrier wait that also records where it gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned where) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  atomicExch(&g_lb_dev_status[0], 1u);
-  atomicExch(&g_lb_dev_status[1], where);
+  if (bw::mbar_wait(bar, parity, abort_flag)) return true;
+  if (atomicCAS(&g_lb_dev_status[0], 0u, 1u) == 0u) atomicExch(&g_lb_dev_status[1], where);
   return false;
 }
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-      "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
-      : "memory");
-}
-// Arrives on the mbarrier once every MMA issued so far by this thread has completed.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor (sm_100 format, 128-byte swizzle).
-//   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4
-//   bits [32,46) stride byte offset >> 4   bits [46,48) version = 1      bits [61,64) layout = 2 (SWIZZLE_128B)
-// K-major tile  [rows][64 elems]: 8-row groups are 1024 B apart (SBO); LBO is unused (1).
-// MN-major tile [k rows][64 elems] per 64-wide MN group: groups are `lbo` bytes apart, 8-k-row
-// groups 1024 B apart (SBO).
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
+__device__ __forceinline__ void tcgen05_fence_before() { fence_before(); }
+__device__ __forceinline__ void tcgen05_fence_after() { fence_after(); }
 
 struct GemmParams {
   int M, N, K;
@@ -143,11 +68,12 @@ struct GemmParams {
 //     so a few CTAs saturate NVLink, which latency-bound remote loads cannot) and count each
 //     128-row block in the destination's flag word; the other CTAs run the tcgen05 main loop,
 //     local rows first (read straight from x_local), each remote tile gated on its flag.
-//   MODE 2, GEMM -> reduce-scatter:  every rank computes partial C = A_local B_local^T [M, N];
-//     the epilogue stages each tile in shared memory and stores it, 512 contiguous bytes per
-//     row, straight into the owner's receive area, counts it in the owner's flag word, and after
-//     its last tile every CTA reduces the row blocks this rank owns as soon as all partials of a
-//     block have arrived.
+//   MODE 2, GEMM -> reduce-scatter:  every rank computes partial C = A_local B_local^T [M, N].
+//     Tiles of rows that another rank keeps come first: the epilogue stages each in shared memory
+//     and stores it, 512 contiguous bytes per row, straight into the owner's receive area and
+//     counts it in the owner's flag word.  Tiles of the rows this rank keeps come last: their
+//     epilogue waits (bounded) for the peers' partials of that row block, adds them to the
+//     accumulator and stores the final bf16 rows, so the reduction costs no extra pass.
 constexpr int MAX_RANKS = 8;
 constexpr int MOVER_WARPS = NUM_THREADS / 32;
 struct CommParams {
@@ -163,6 +89,7 @@ struct CommParams {
   unsigned int* rs_flags[MAX_RANKS];                   // MODE 2: rank r's counters [n_ranks][blocks_per_rank]
   bf16* out;                                           // MODE 2: reduced [rows_per_rank, N]
   long long ld_out;
+  unsigned long long wait_ns;                          // limit of every wait on a peer's flag
 };
 
 __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& tm, int& tn) {
@@ -175,35 +102,10 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& tm,
   tn = in_group / gsz;
 }
 
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ void red_release_sys_add(unsigned int* p, unsigned int v) {
-  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait on a flag written by another CTA or another GPU: gives up after ~20 s of wall
-// time (ranks may be skewed by seconds at start-up), records the failure and returns false.
-constexpr unsigned long long FLAG_WAIT_NS = 20ull * 1000ull * 1000ull * 1000ull;
-__device__ __forceinline__ bool flag_wait_ge(const unsigned int* f, unsigned int target, unsigned where) {
-  if ((int)(ld_acquire_sys(f) - target) >= 0) return true;
-  const unsigned long long t0 = globaltimer_ns();
-  while (true) {
-    for (int i = 0; i < 64; i++) {
-      if ((int)(ld_acquire_sys(f) - target) >= 0) return true;
-      __nanosleep(64);
-    }
-    if (globaltimer_ns() - t0 > FLAG_WAIT_NS) break;
-  }
+using lbcomm::red_release_sys_add;
+// Bounded wait on a flag written by another CTA or another GPU; records the failure.
+__device__ __forceinline__ bool flag_wait_ge(const unsigned int* f, unsigned int target, unsigned long long limit_ns, unsigned where) {
+  if (lbcomm::flag_wait_ge(f, target, limit_ns)) return true;
   atomicExch(&g_lb_dev_status[0], 2u);
   atomicExch(&g_lb_dev_status[1], where);
   return false;
@@ -215,22 +117,6 @@ constexpr int RS_ROW_BYTES = BN * 2 + 16;                 // padded: 16-byte sto
 constexpr int RS_STAGE_BYTES = 4 * 32 * RS_ROW_BYTES;
 constexpr int STAGES_RS = 3;
 constexpr int SMEM_BYTES_RS = STAGES_RS * STAGE_BYTES + 1024 + 1024 + RS_STAGE_BYTES;
-// mover CTAs of MODE 1: ring of bulk-copy buffers
-constexpr int MV_BUF_BYTES = 32 * 1024;
-constexpr int MV_NBUF = 5;
-
-__device__ __forceinline__ void bulk_load(uint32_t sdst, const void* gsrc, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(sdst),
-               "l"(gsrc), "r"(bytes), "r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_store(void* gdst, uint32_t ssrc, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(ssrc), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
 // One tile of the producer / of the MMA issuer with the operand majors as compile-time constants:
 // descriptor fields and the number of TMA boxes become constants in the single-thread issue loops
 // (measured 3-8 % faster than run-time majors).
@@ -376,13 +262,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), 4);
     }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+    mbar_init_fence();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
   }
   if (warp == 1) {  // allocate all 512 TMEM columns (one CTA per SM by construction)
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tmem_alloc(smem_u32(tmem_slot), 512);
   }
   tcgen05_fence_before();
   __syncthreads();
@@ -406,7 +291,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (!own) {
             // rows of this tile must have landed in this rank's gather buffer (pushed by a peer):
             // acquire the flag, then order those writes before the async-proxy reads
-            if (!flag_wait_ge(cp.ag_flags[cp.rank] + tm, cp.ag_target, 11u)) { *abort_flag = 1; ok = false; break; }
+            if (!flag_wait_ge(cp.ag_flags[cp.rank] + tm, cp.ag_target, cp.wait_ns, 11u)) { *abort_flag = 1; ok = false; break; }
             asm volatile("fence.proxy.async;" ::: "memory");
           }
         }
@@ -470,6 +355,45 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         crow = cp.recv[owner] + ((size_t)cp.rank * cp.rows_per_rank + (size_t)lb * BM + quad * 32 + lane) * p.N + n0;
       } else {
         crow = C + (size_t)row * p.ldc + n0;
+      }
+      if (MODE == 2 && owner == cp.rank) {
+        // Rows that this rank keeps (its tiles come last in the tile order, so the peers' partials of
+        // these rows, which they produce FIRST, have normally landed in the receive area long ago):
+        // wait for them, add them to the accumulator and store the finished bf16 rows.  No trip
+        // through the receive area for the own partial, no second kernel for the sum.
+        bool arrived = true;
+        for (int s = 0; s < cp.n_ranks; s++)
+          if (s != cp.rank && !flag_wait_ge(cp.rs_flags[cp.rank] + s * cp.blocks_per_rank + lb, cp.rs_target, cp.wait_ns, 21u))
+            arrived = false;
+        const size_t lrow = (size_t)lb * BM + quad * 32 + lane;           // row inside this rank's [rows_per_rank, N]
+        bf16* orow = cp.out + lrow * cp.ld_out + n0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; c++) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            const int col = n0 + c * 32 + g * 8;
+            if (col < p.N && arrived) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[g * 8 + i]);
+              for (int s = 0; s < cp.n_ranks; s++) {
+                if (s == cp.rank) continue;
+                float o[8];
+                unpack8(__ldcg(reinterpret_cast<const uint4*>(cp.recv[cp.rank] + ((size_t)s * cp.rows_per_rank + lrow) * p.N + col)), o);
+#pragma unroll
+                for (int i = 0; i < 8; i++) f[i] += o[i];
+              }
+              *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = pack8(f);
+            }
+          }
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+        continue;
       }
       if (MODE == 2) {
         // TMEM -> registers -> padded smem panel of this warp -> one bulk store per row (512 B) to
@@ -550,75 +474,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    tmem_dealloc(tmem_base, 512);
   }
 
-  if (MODE == 2) {
-    // ---------------- wait until every partial of the rows this rank owns has arrived ----------------
-    // (the kernel's completion then means "receive area complete"; the n-way sum runs as a plain
-    // bandwidth-bound kernel right behind it, with the whole GPU instead of a tail of this grid)
-    const int n_flags = cp.n_ranks * cp.blocks_per_rank;
-    for (int i = blockIdx.x * NUM_THREADS + threadIdx.x; i < n_flags; i += gridDim.x * NUM_THREADS)
-      flag_wait_ge(cp.rs_flags[cp.rank] + i, cp.rs_target, 20u);
-  }
-}
-
-// out[r, c] = sum over source ranks of recv[s][r, c]; recv is this rank's receive area.
-__global__ void rs_reduce_kernel(const bf16* __restrict__ recv, bf16* __restrict__ out, int n_ranks, int rows, int N,
-                                 long long ld_out) {
-  const int vec_per_row = N / 8;
-  const long long total = (long long)rows * vec_per_row;
-  const size_t plane = (size_t)rows * N;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const long long r = i / vec_per_row;
-    const int v = (int)(i % vec_per_row);
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < n_ranks; s++) {
-      float f[8];
-      unpack8(__ldcg(reinterpret_cast<const uint4*>(recv + s * plane + (size_t)r * N + v * 8)), f);
-#pragma unroll
-      for (int k = 0; k < 8; k++) acc[k] += f[k];
-    }
-    *reinterpret_cast<uint4*>(out + r * ld_out + v * 8) = pack8(acc);
-  }
 }
 
 // ---- host side --------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-
 // 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows of `ld` elements.
 int make_map(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
              uint32_t box_outer) {
-  EncodeTiledFn enc = get_encode();
-  if (!enc) return LB_ERR_DRIVER;
-  cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {ld * 2};
-  cuuint32_t box[2] = {box_inner, box_outer};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    g_lb_last_cuda_error = (int)r;
-    return LB_ERR_TMAP;
-  }
-  return LB_OK;
+  return bw::make_map_bf16(m, base, inner, outer, ld, box_inner, box_outer);
 }
 
 int g_num_sms = 0;
@@ -743,7 +608,7 @@ extern "C" int lb_gemm_ag(const void* B, void* C, int M, int N, int K, long long
   cp.n_ranks = n_ranks; cp.rank = rank; cp.rows_per_rank = M / n_ranks; cp.blocks_per_rank = cp.rows_per_rank / BM;
   if (n_comm < 1) n_comm = 1;
   if (n_comm > sms / 2) n_comm = sms / 2;
-  cp.n_comm = n_comm; cp.ag_target = ag_target;
+  cp.n_comm = n_comm; cp.ag_target = ag_target; cp.wait_ns = g_lb_flag_wait_ns;
   cp.x_local = (const bf16*)x_local; cp.ld_x = ld_x;
   for (int r = 0; r < n_ranks; r++) { cp.gather[r] = (bf16*)gather_ptrs[r]; cp.ag_flags[r] = (unsigned int*)flag_ptrs[r]; }
   int n_gemm = sms - n_comm;
@@ -779,15 +644,11 @@ extern "C" int lb_gemm_rs(const void* A, const void* B, int M, int N, int K, lon
   CommParams cp;
   memset(&cp, 0, sizeof(cp));
   cp.n_ranks = n_ranks; cp.rank = rank; cp.rows_per_rank = M / n_ranks; cp.blocks_per_rank = cp.rows_per_rank / BM;
-  cp.rs_target = rs_target;
+  cp.rs_target = rs_target; cp.wait_ns = g_lb_flag_wait_ns;
   for (int r = 0; r < n_ranks; r++) { cp.recv[r] = (bf16*)recv_ptrs[r]; cp.rs_flags[r] = (unsigned int*)flag_ptrs[r]; }
   cp.out = (bf16*)out; cp.ld_out = ld_out;
   int grid = p.num_tiles < sms ? p.num_tiles : sms;
   gemm_bf16_kernel<2><<<grid, NUM_THREADS, SMEM_BYTES_RS, (cudaStream_t)stream>>>(ta, tb, ta, nullptr, p, cp);
-  LB_CHECK_LAUNCH();
-  const long long total = (long long)cp.rows_per_rank * (N / 8);
-  int rblocks = (int)((total + 255) / 256 > sms * 8 ? sms * 8 : (total + 255) / 256);
-  rs_reduce_kernel<<<rblocks, 256, 0, (cudaStream_t)stream>>>(cp.recv[rank], cp.out, n_ranks, cp.rows_per_rank, N, ld_out);
   LB_CHECK_LAUNCH();
   return LB_OK;
 }

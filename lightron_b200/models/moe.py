@@ -35,6 +35,22 @@ class MoEFeedForward(nn.Module):
         self.sp = args.sequence_parallel and args.tp_size > 1
         self.tp_group = ctx.tp_group if args.tp_size > 1 else None
         self.last_aux_loss = None
+        self.capacity_factor = args.moe_capacity_factor
+        self.pp_size = getattr(ctx, "pp_size", 1)
+        self.layer_key = id(self)
+
+    def _fused_ok(self, x: torch.Tensor) -> bool:
+        """The kernel chain of ``parallel.ep_fused`` (router, peer-memory dispatch / combine, ragged
+        expert GEMMs, no host synchronisation): CUDA bf16, experts not tensor-parallel, parameters in
+        the flat arena, and no pipeline parallelism (several micro-batches between a layer's forward
+        and backward would share the layer's exchange buffers)."""
+        from ..parallel import ep_fused
+        if self.tp_group is not None or self.pp_size > 1:
+            return False
+        mlps = list(self.experts.values())
+        if not all(OF._rows_adjacent((m.w1.weight, m.w3.weight)) for m in mlps):
+            return False
+        return ep_fused.supported(x, self.ep.group, self.num_experts, self.topk, self.ep.local_experts)
 
     def _apply_experts(self, tokens: torch.Tensor, meta) -> torch.Tensor:
         """Local expert e on its contiguous segment of ``tokens``: one grouped GEMM launch for the
@@ -61,6 +77,15 @@ class MoEFeedForward(nn.Module):
         if self.sp:                       # experts see whole tokens; gather the row shards first
             x = comm.gather_rows_replicated(x, self.tp_group)
         T, H = x.shape
+        if self._fused_ok(x):
+            from ..parallel import ep_fused
+            ws = [w for m in self.experts.values() for w in (m.w1.weight, m.w3.weight, m.w2.weight)]
+            out, aux = ep_fused.fused_moe(x, self.gate.weight, ws, self.num_experts, self.topk, self.ep.group,
+                                          self.layer_key, self.capacity_factor)
+            self.last_aux_loss = aux[0]
+            if self.sp:
+                out = comm.split_rows(out, self.tp_group)
+            return out
         logits = OF.linear(x, self.gate.weight).float()
         probs = F.softmax(logits, dim=-1)
         weights, indices = torch.topk(probs, self.topk, dim=-1)

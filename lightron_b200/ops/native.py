@@ -31,6 +31,8 @@ _P, _I, _L, _F = c_void_p, c_int, c_int64, c_float
 # name -> argtypes (all return int)
 _SIGNATURES = {
     "lb_last_error": [],
+    "lb_sm_count": [],
+    "lb_set_flag_wait_ns": [ctypes.c_ulonglong],
     "lb_device_status": [_P],
     "lb_rmsnorm_fwd": [_P, _P, _P, _P, _P, _P, _I, _I, _F, _P],
     "lb_rmsnorm_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
@@ -48,9 +50,25 @@ _SIGNATURES = {
     "lb_gemm_bf16": [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _I, _P],
     "lb_gemm_grouped": [_I] + [_P] * 13,
     "lb_gemm_grouped_status": [_P],
+    "lb_gemm_grouped_cached": [],
     "lb_gemm_grouped_plan": [_I, _P, _P, _P, _I, _P],
     "lb_gemm_ag": [_P, _P, _I, _I, _I, _L, _L, _I, _I, _I, _P, _L, _P, _P, ctypes.c_uint, _I, _P],
     "lb_gemm_rs": [_P, _P, _I, _I, _I, _L, _L, _I, _I, _I, _P, _P, ctypes.c_uint, _P, _L, _P],
+    "lb_moe_status": [_P],
+    "lb_moe_router_blocks": [_I],
+    "lb_moe_push_ctas": [_I],
+    "lb_moe_router": [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
+    "lb_moe_plan": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _I, ctypes.c_uint, _P],
+    "lb_moe_push": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P],
+    "lb_moe_pull": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, ctypes.c_uint, _P],
+    "lb_moe_router_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "lb_gemm_ragged": [_P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P, ctypes.c_uint, _P],
+    "lb_gemm_ragged_wgrad": [_P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P],
+    "lb_swiglu_fwd_dev": [_P, _P, _I, _I, _L, _P, _P],
+    "lb_swiglu_bwd_dev": [_P, _P, _P, _I, _I, _L, _P, _P],
+    "lb_coll_status": [_P],
+    "lb_collective": [_I, _P, _P, _P, _P, _L, _L, _I, _I, _I, _I, ctypes.c_uint, _P],
+    "lb_all_reduce_nvls": [_P, _P, _P, _P, _P, _L, _L, _I, _I, _I, _I, ctypes.c_uint, _P],
     "lb_dp_status": [_P],
     "lb_dp_adamw": [_P, _P, _P, _P, _P, _P, _P, _L, _L, _I, _I, ctypes.c_uint, _F, _F, _F, _F, _F, _F, _F, _F, _I, _P],
     "lb_flash_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _P],
@@ -112,6 +130,33 @@ def use_native(t: torch.Tensor) -> bool:
     return True
 
 
+def sm_count() -> int:
+    """SMs of the current device (what the persistent kernels size their grids with)."""
+    return int(require().lb_sm_count())
+
+
+def set_flag_wait_ns(ns: int) -> None:
+    """Wall-time limit after which a kernel that waits for a peer's flag gives up and reports through
+    its status word (default 20 s; tests of the give-up path use a few milliseconds)."""
+    rc = require().lb_set_flag_wait_ns(int(ns))
+    if rc != 0:
+        raise NativeError(f"lb_set_flag_wait_ns({ns}) failed: {rc}")
+
+
+def measured_peaks() -> dict:
+    """``MEASURED_PEAKS.json`` at the repository root when present (roofline denominators measured on
+    the machine: ``hbm_gbs``, ``bf16_tflops``, ``bf16_tflops_sustained``), else the nominal figures."""
+    import json
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        d["source"] = "measured"
+        return d
+    except Exception:
+        return {"hbm_gbs": 7700.0, "bf16_tflops": 2250.0, "bf16_tflops_sustained": 2250.0, "source": "nominal"}
+
+
 def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -146,7 +191,9 @@ def call(name: str, *args) -> None:
 
 _STATUS_READERS = (("lb_device_status", "GEMM / fused collective GEMM"), ("lb_gemm_grouped_status", "grouped GEMM"),
                    ("lb_flash_status", "attention forward"), ("lb_flash_bwd_status", "attention backward"),
-                   ("lb_dp_status", "data-parallel optimizer kernel"))
+                   ("lb_dp_status", "data-parallel optimizer kernel"),
+                   ("lb_moe_status", "expert-parallel routing / dispatch / combine"),
+                   ("lb_coll_status", "stand-alone peer-memory collective"))
 
 
 def device_status() -> dict:

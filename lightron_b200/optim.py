@@ -205,7 +205,7 @@ class DistributedAdamW:
         grads = buf[head + total * 2:head + 4 * total].view(dtype)
         self.fused_dp = {"buf": buf, "hdl": hdl, "flags": mk(0), "params": mk(head), "grads": mk(head + total * 2),
                          "counter": torch.zeros(1, dtype=torch.int32, device=device), "epoch": 0,
-                         "rank": dist.get_rank(group), "n": n}
+                         "rank": dist.get_rank(group), "n": n, "grid": native.sm_count() * 8}
         return flat, grads
 
     # ---- gradient synchronisation ---------------------------------------------------------
@@ -321,7 +321,7 @@ class DistributedAdamW:
             native.call("lb_dp_adamw", f["grads"], f["params"], f["flags"], f["counter"].data_ptr(),
                         self.master.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
                         b.start + f["rank"] * b.shard_len, b.shard_len, f["n"], f["rank"], f["epoch"], self.lr, b1, b2,
-                        self.eps, self.weight_decay, bc1, bc2, scale, 148 * 8, native.stream_ptr())
+                        self.eps, self.weight_decay, bc1, bc2, scale, f["grid"], native.stream_ptr())
             self._reset_buckets()
             return
         if self.native:

@@ -102,7 +102,23 @@ class Trainer:
                 symm.presize(ctx.tp_group, tokens, self.args.dim, self.device, fwd_gathers_in_flight=per_mb * in_flight)
         self.step = 0
         self.tokens_seen = 0
+        # MFU denominator: the bf16 matmul rate measured on this machine under sustained load when the
+        # measurement file is present, else the nominal dense figure
+        peaks = native.measured_peaks()
+        self.peak_flops = float(peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]) * 1e12
+        self.peak_source = peaks["source"]
         self.timer = StepTimer(self.device)
+        # liveness: every rank publishes a beat in the rendezvous store at each log interval and looks
+        # at the others' (health.Heartbeat); a rank that stopped beating is reported on the host before
+        # the next collective would hang on it
+        self.heartbeat = None
+        if dist.is_initialized() and ctx.world_size > 1 and t.heartbeat_timeout_s > 0:
+            try:
+                store = dist.distributed_c10d._get_default_store()
+                self.heartbeat = health.Heartbeat(store, ctx.rank, ctx.world_size)
+                self.heartbeat.beat()
+            except Exception:
+                self.heartbeat = None
         if t.resume:
             meta = ckpt.load(t.resume, self.model, self.optimizer, self.dataloader, ctx)
             self.step, self.tokens_seen = meta["trained_steps"], meta["trained_tokens"]
@@ -129,9 +145,24 @@ class Trainer:
         self.tokens_seen += self.dataloader.global_batch_size * t.seq_length
         return loss
 
+    def _check_liveness(self) -> None:
+        """Beat, then fail loudly if a rank has not beaten for ``heartbeat_timeout_s`` (it died or is
+        stuck between steps; the survivors would otherwise sit in the next collective until its timeout)."""
+        hb = self.heartbeat
+        if hb is None:
+            return
+        from . import health
+        hb.beat()
+        dead = hb.dead_ranks(self.cfg.training.heartbeat_timeout_s)
+        if dead:
+            raise health.RankFailure(f"ranks {dead} have not published a heartbeat for more than "
+                                     f"{self.cfg.training.heartbeat_timeout_s:.0f} s")
+
     def save(self, path: Optional[str] = None) -> str:
         d = self.cfg.distributed
         path = path or ckpt.ckpt_name(self.step, d.tp_size, d.dp_size, self.cfg.training.save_dir)
+        if self.device.type == "cuda" and native.available():
+            native.raise_on_device_status()        # never checkpoint state that a timed-out kernel may have skipped
         ckpt.save(path, self.model, self.optimizer, self.step, self.tokens_seen, self.dataloader, self.ctx)
         return path
 
@@ -165,18 +196,20 @@ class Trainer:
                 last_loss = float(loss)                            # the only host sync, once per log interval
                 if self.device.type == "cuda" and native.available():
                     native.raise_on_device_status()                # bounded waits that ran out inside a kernel
+                self._check_liveness()
                 if is_log:
                     tps_wall = (self.tokens_seen - tokens0) / max(time.time() - start, 1e-9)
                     tps_dev = tokens_per_step / (ms / 1e3) if ms > 0 else float("nan")
                     # model FLOPs: 6 N per token for the matmuls + causal attention (fwd + bwd)
                     a = self.args
                     flops_tok = 6.0 * a.num_active_params() + 6.0 * a.n_layers * a.dim * t.seq_length
-                    mfu = flops_tok * tps_dev / (ctx.world_size * 2.25e15) if ms > 0 else float("nan")
+                    mfu = flops_tok * tps_dev / (ctx.world_size * self.peak_flops) if ms > 0 else float("nan")
                     print(f"Step {self.step}/{t.total_steps} | Loss: {last_loss:.4f} | TPS: {tps_wall:.2f} tokens/s"
                           f" | device TPS: {tps_dev:.2f} | step {ms:.2f} ms | MFU {mfu * 100:.1f}%", flush=True)
                     if log_f:
                         log_f.write(json.dumps({"step": self.step, "loss": last_loss, "tokens_per_s_wall": tps_wall,
-                                                "tokens_per_s_device": tps_dev, "step_ms": ms, "mfu_vs_2.25PF": mfu,
+                                                "tokens_per_s_device": tps_dev, "step_ms": ms, "mfu": mfu, "mfu_peak_tflops": self.peak_flops / 1e12,
+                                                "mfu_peak_source": self.peak_source,
                                                 "tokens_seen": self.tokens_seen}) + "\n")
                         log_f.flush()
                 self.timer.reset()

@@ -191,3 +191,45 @@ def test_host_side_failure_detection():
     assert res[0]["mismatch"] and res[1]["mismatch"]
     assert res[0]["dead"] == [1]
     assert res[0]["guard"] == "timeout"
+
+
+_RESHARD = {
+    "distributed": {},
+    "model": {"name": "tiny"},
+    "dataset": {"name": "synthetic"},
+    "training": {"micro_batch_size": 2, "gradient_accumulation_steps": 1, "seq_length": 64, "learning_rate": 3e-4,
+                 "total_steps": 2, "seed": 0, "dtype": "fp32", "log_interval": 1000},
+}
+
+
+def _reshard_worker(rank, world, tmp, phase):
+    import copy
+    import warnings
+    from lightron_b200.config import parse_config
+    from lightron_b200.trainer import Trainer
+    raw = copy.deepcopy(_RESHARD)
+    if phase == "save":
+        raw["distributed"]["tp_size"] = 2
+        raw["training"]["save_dir"] = tmp
+        out = Trainer(parse_config(raw, env={})).fit()
+        return out["checkpoint"]
+    raw["distributed"]["dp_size"] = 2
+    raw["training"].update(resume=os.path.join(tmp, "ckpt_step_2_tpsize_2_dpsize_1"), total_steps=3, save_final=False)
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        tr = Trainer(parse_config(raw, env={}))
+    warned = any("parallel layout" in str(x.message) for x in w)
+    loss = float(tr.train_step())
+    return warned, tr.step, tr.dataloader.cursor, loss, int(tr.optimizer.step_count)
+
+
+def test_checkpoint_resumes_under_another_layout(tmp_path):
+    """Saved at tp=2, resumed at dp=2: the per-rank optimizer shards, RNG state and data cursor of
+    the old layout must not be loaded into ranks that mean something else now."""
+    run_distributed(_reshard_worker, 2, str(tmp_path), "save")
+    res = run_distributed(_reshard_worker, 2, str(tmp_path), "load")
+    for warned, step, cursor, loss, opt_steps in res:
+        assert warned
+        assert step == 3 and cursor == 3          # cursor recomputed from the step count (2), then one more batch
+        assert opt_steps == 1                       # moments restarted
+        assert loss == loss and loss < 20.0

@@ -298,3 +298,57 @@ def test_rope_attention_on_fused_qkv():
     of.backward(do.float())
     assert _rel_err(o, of) < 1e-2
     assert _rel_err(x.grad, xf.grad) < 2e-2
+
+
+@pytest.mark.parametrize("B,S,hq,hkv,d", [(1, 2048, 8, 1, 64), (1, 8192, 8, 1, 128), (2, 1000, 8, 1, 64), (1, 777, 4, 4, 128)])
+def test_flash_attention_long_sequences(B, S, hq, hkv, d):
+    """Sequence lengths of the benchmark shapes (16 and 64 key blocks: the K/V and Q/dO stage rings
+    wrap many times, query tiles differ by many key blocks), hq / hkv = 8, lengths that are not
+    multiples of 128; forward and every gradient against the fp32 oracle."""
+    from lightron_b200.ops import functional as OF, reference as ref
+    q = _rand(B, S, hq, d, seed=1).requires_grad_(True)
+    k = _rand(B, S, hkv, d, seed=2).requires_grad_(True)
+    v = _rand(B, S, hkv, d, seed=3).requires_grad_(True)
+    o = OF.flash_attention(q, k, v, True)
+    do = _rand(B, S, hq, d, seed=4)
+    o.backward(do)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    of = ref.attention(qf, kf, vf, causal=True)
+    of.backward(do.float())
+    torch.cuda.synchronize()
+    from lightron_b200.ops import native
+    assert not native.device_status()
+    assert _rel_err(o, of) < 1e-2, f"fwd {_rel_err(o, of)}"
+    assert _rel_err(q.grad, qf.grad) < 2e-2, f"dq {_rel_err(q.grad, qf.grad)}"
+    assert _rel_err(k.grad, kf.grad) < 2e-2, f"dk {_rel_err(k.grad, kf.grad)}"
+    assert _rel_err(v.grad, vf.grad) < 2e-2, f"dv {_rel_err(v.grad, vf.grad)}"
+
+
+def test_peer_wait_runs_out_and_reports():
+    """A device-side wait on a peer that never arrives: with a limit of a few milliseconds the
+    kernel returns, the status word is set, the host raises, and nothing was updated.  The 'peer'
+    is a second rank of the data-parallel optimizer kernel that is simply never launched (its flag
+    word stays 0); both ranks' arenas live on this one GPU."""
+    import ctypes
+    from lightron_b200.ops import native
+    n = 4096
+    grads = [torch.ones(n, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    params = [torch.full((n,), 3.0, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(16, dtype=torch.int32, device="cuda") for _ in range(2)]
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    master = torch.full((n // 2,), 3.0, device="cuda")
+    m, v = torch.zeros_like(master), torch.zeros_like(master)
+    arr = lambda ts: (ctypes.c_void_p * 2)(*[t.data_ptr() for t in ts])
+    native.device_status()                                   # clear
+    native.set_flag_wait_ns(5_000_000)                       # 5 ms
+    try:
+        native.call("lb_dp_adamw", arr(grads), arr(params), arr(flags), counter.data_ptr(), master.data_ptr(), m.data_ptr(),
+                    v.data_ptr(), 0, n // 2, 2, 0, 1, 1e-2, 0.9, 0.999, 1e-8, 0.0, 0.1, 0.001, 1.0, 4, native.stream_ptr())
+        torch.cuda.synchronize()                             # the kernel came back by itself
+    finally:
+        native.set_flag_wait_ns(20_000_000_000)
+    assert float(master.min()) == 3.0 and float(master.max()) == 3.0          # update skipped
+    assert float(m.abs().max()) == 0.0 and float(params[1].float().min()) == 3.0
+    with pytest.raises(RuntimeError, match="data-parallel optimizer"):
+        native.raise_on_device_status()
+    assert not native.device_status()                        # reading cleared it

@@ -31,7 +31,12 @@ for _ in range(steps):
 if tr.args.sequence_parallel and tr.ctx.tp_size > 1:
     from lightron_b200.parallel import symm
     symm.check_status()
+from lightron_b200 import checkpoint
+from lightron_b200.ops import native
+native.raise_on_device_status()
+sd = checkpoint.full_state_dict(tr.model, tr.ctx)          # collective: every rank takes part
 if tr.ctx.rank == 0:
+    torch.save({k: v.float() for k, v in sd.items()}, os.environ["LB_DUMP"])
     print("LOSSES " + json.dumps(losses), flush=True)
 mesh.destroy()
 '''
@@ -45,34 +50,51 @@ BASE = {
 }
 
 
-def _run(tmp_path, world, dist_kw, train_kw=None, model_kw=None, steps=3, port=29550):
+def _run(tmp_path, world, dist_kw, train_kw=None, model_kw=None, steps=3, port=29550, env_extra=None, tag="run"):
     raw = json.loads(json.dumps(BASE))
     raw["distributed"].update(dist_kw)
     raw["training"].update(train_kw or {})
     raw["model"].update(model_kw or {})
     script = tmp_path / "w.py"
     script.write_text(WORKER)
+    dump = str(tmp_path / f"{tag}_{world}.pt")
     env = dict(os.environ, REPO=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), LB_CFG=json.dumps(raw),
-               LB_STEPS=str(steps), NCCL_NVLS_ENABLE="0")
+               LB_STEPS=str(steps), NCCL_NVLS_ENABLE="0", LB_DUMP=dump)
+    env.update(env_extra or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
            "127.0.0.1", "--master-port", str(port), str(script)]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-2500:] + r.stderr[-2500:]
     line = [l for l in r.stdout.splitlines() if l.startswith("LOSSES ")][-1]
-    return json.loads(line[len("LOSSES "):])
+    return json.loads(line[len("LOSSES "):]), torch.load(dump)
 
 
-def _check(tmp_path, world, dist_kw, train_kw=None, model_kw=None, tol=3e-2):
+def _compare_params(got, want, tol):
+    """Every tensor of the full (unsharded) state_dict after the steps.  Three AdamW steps at
+    lr 1e-3 move a weight of scale 0.02 by about 15 %; two correct bf16 runs end within a fraction
+    of a percent of each other, while a gradient that missed a reduction (or was reduced over the
+    wrong group) moves its tensor somewhere else by several percent."""
+    assert set(got) == set(want)
+    bad = []
+    for k in sorted(want):
+        err = ((got[k] - want[k]).norm() / want[k].norm().clamp_min(1e-9)).item()
+        if err > tol:
+            bad.append((k, round(err, 4)))
+    assert not bad, f"parameters differ from the single-GPU run: {bad[:8]}"
+
+
+def _check(tmp_path, world, dist_kw, train_kw=None, model_kw=None, tol=3e-2, param_tol=2e-2):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     dp = dist_kw.get("dp_size", 1)
     tk = dict(train_kw or {})
     ga = tk.get("gradient_accumulation_steps", 1)
     single_kw = dict(tk, gradient_accumulation_steps=ga * dp)      # same global batch, same sample order
-    want = _run(tmp_path, 1, {}, single_kw, model_kw, port=29551)
-    got = _run(tmp_path, world, dist_kw, tk, model_kw, port=29552)
+    want, sd_want = _run(tmp_path, 1, {}, single_kw, model_kw, port=29551, tag="single")
+    got, sd_got = _run(tmp_path, world, dist_kw, tk, model_kw, port=29552, tag="multi")
     for a, b in zip(got, want):
         assert abs(a - b) < tol * max(1.0, abs(b)), f"{got} vs {want}"
+    _compare_params(sd_got, sd_want, param_tol)
 
 
 def test_tp2_sequence_parallel_fused(tmp_path):
@@ -115,3 +137,28 @@ def test_tp2_dp2_fused(tmp_path):
 def test_tp2_pp2(tmp_path):
     _check(tmp_path, 4, {"tp_size": 2, "pp_size": 2, "sequence_parallel": True},
            {"gradient_accumulation_steps": 4, "micro_batch_size": 1})
+
+
+def test_ep2_kernel_chain_matches_library_path(tmp_path):
+    """Expert parallelism on 2 GPUs: peer-memory dispatch / combine kernels against the NCCL
+    all-to-all path, parameters after 3 steps."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    kw = dict(dist_kw={"dp_size": 2, "ep_size": 2},
+              model_kw={"moe_num_experts": 4, "moe_topk": 2, "moe_layer_freq": 2, "moe_aux_loss_coef": 0.01})
+    l_lib, sd_lib = _run(tmp_path, 2, kw["dist_kw"], None, kw["model_kw"], port=29553, env_extra={"LIGHTRON_FUSED_EP": "0"}, tag="lib")
+    l_k, sd_k = _run(tmp_path, 2, kw["dist_kw"], None, kw["model_kw"], port=29554, tag="kernels")
+    for a, b in zip(l_k, l_lib):
+        assert abs(a - b) < 3e-2 * max(1.0, abs(b)), f"{l_k} vs {l_lib}"
+    _compare_params(sd_k, sd_lib, 2e-2)
+
+
+def test_gradient_accumulation_in_bf16_arena(tmp_path):
+    """Eight micro-batches accumulate into the bf16 gradient arena (the GEMM epilogue adds to it);
+    the result must stay close to one step over the same 8 x batch done as a single micro-batch
+    ... which accumulates nothing.  Bounds the rounding error of bf16 accumulation at GA = 8."""
+    one, sd_one = _run(tmp_path, 1, {}, {"micro_batch_size": 8, "gradient_accumulation_steps": 1}, None, port=29555, tag="ga1")
+    acc, sd_acc = _run(tmp_path, 1, {}, {"micro_batch_size": 1, "gradient_accumulation_steps": 8}, None, port=29556, tag="ga8")
+    for a, b in zip(acc, one):
+        assert abs(a - b) < 3e-2 * max(1.0, abs(b)), f"{acc} vs {one}"
+    _compare_params(sd_acc, sd_one, 2e-2)
