@@ -40,6 +40,12 @@ def full_state_dict(model: nn.Module, ctx: Optional[_mesh.ParallelContext] = Non
     with ``all_gather_object``."""
     ctx = ctx or getattr(model, "ctx", None) or _mesh.get_context()
     stage = getattr(model, "stage", model)
+    # sharded-parameter engines: a parameter's storage holds its values only while its block is gathered
+    if getattr(stage, "_fsdp_native", None) is not None:
+        out = stage._fsdp_native.full_state_dict()
+        return _merge_over_groups(out, ctx)
+    if getattr(stage, "_fsdp", None) is not None:
+        return {k: v.cpu() for k, v in stage._fsdp.full_state_dict().items()}
     out: Dict[str, torch.Tensor] = {}
     for name, p in stage.named_parameters():
         t = p.detach()
@@ -49,6 +55,11 @@ def full_state_dict(model: nn.Module, ctx: Optional[_mesh.ParallelContext] = Non
             dist.all_gather(parts, t.contiguous(), group=ctx.tp_group)
             t = torch.cat(parts, dim=dim)
         out[name] = t.cpu().clone()
+    return _merge_over_groups(out, ctx)
+
+
+def _merge_over_groups(out: Dict[str, torch.Tensor], ctx) -> Dict[str, torch.Tensor]:
+    """Pipeline stages and expert-parallel ranks hold different parameters: union of their dicts."""
     for group, n in ((ctx.ep_group, ctx.ep_size), (ctx.pp_group, ctx.pp_size)):
         if n > 1:
             gathered = [None] * n
@@ -65,6 +76,8 @@ def load_full_state_dict(model: nn.Module, sd: Dict[str, torch.Tensor], ctx=None
     """Copy a full (unsharded) state_dict into this rank's shards."""
     ctx = ctx or getattr(model, "ctx", None) or _mesh.get_context()
     stage = getattr(model, "stage", model)
+    if getattr(stage, "_fsdp_native", None) is not None:
+        return stage._fsdp_native.load_full_state_dict(sd)
     missing = []
     for name, p in stage.named_parameters():
         if name not in sd:

@@ -222,6 +222,209 @@ __global__ void __launch_bounds__(COLL_THREADS) all_reduce_nvls_kernel(const Col
     *reinterpret_cast<uint4*>(out + e) = __ldcv(reinterpret_cast<const uint4*>(mine + e));
 }
 
+// ---- all-gather straight into a peer-visible destination that is reused (parameter gather of the
+// sharded engine).  Every rank stores slice b of its shard at offset me * shard into every rank's
+// destination, but only after every rank has released the destination's previous contents: the
+// `free` words [n] of this rank hold, per peer, how many uses of the destination that peer has
+// finished (lb_slot_release).  No staging copy: when the kernel ends the destination is complete. -----
+struct GatherParams {
+  const bf16* src;                        // this rank's shard [shard_elems]
+  bf16* dst[COLL_MAX_RANKS];              // rank r's destination [n * shard_elems]
+  unsigned int* arrive[COLL_MAX_RANKS];   // rank r's arrival table [n][G]
+  const unsigned int* free_words;         // this rank's table [n]: uses released by peer r
+  long long shard_elems;
+  int n, me, G;
+  unsigned int use;                       // 1, 2, 3, ... per destination
+  unsigned long long wait_ns;
+};
+
+__global__ void __launch_bounds__(COLL_THREADS) gather_into_kernel(const GatherParams p) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  if (threadIdx.x < p.n && p.use > 1u && !lbcomm::flag_wait_ge(p.free_words + threadIdx.x, p.use - 1u, p.wait_ns)) {
+    s_fail = 1;
+    coll_fail(20u);
+  }
+  __syncthreads();
+  if (s_fail) return;
+  long long lo, hi;
+  slice_of(p.shard_elems, 8, p.G, blockIdx.x, lo, hi);
+  for (long long e = lo + (long long)threadIdx.x * 8; e < hi; e += (long long)COLL_THREADS * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p.src + e);
+    for (int j = 0; j < p.n; j++) {
+      const int r = (p.me + 1 + j) % p.n;             // peers first, the local copy last
+      *reinterpret_cast<uint4*>(p.dst[r] + (long long)p.me * p.shard_elems + e) = v;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < p.n) {
+    __threadfence_system();
+    lbcomm::st_release_sys(p.arrive[threadIdx.x] + ((size_t)p.me * p.G + blockIdx.x), p.use);
+    if (!lbcomm::flag_wait_ge(p.arrive[p.me] + ((size_t)threadIdx.x * p.G + blockIdx.x), p.use, p.wait_ns)) coll_fail(21u);
+  }
+}
+
+struct ReleaseParams { unsigned int* tab[COLL_MAX_RANKS]; int n, me; unsigned int use; };
+__global__ void slot_release_kernel(const ReleaseParams p) {
+  if (threadIdx.x < p.n) {
+    __threadfence_system();
+    lbcomm::st_release_sys(p.tab[threadIdx.x] + p.me, p.use);
+  }
+}
+
+// ---- context parallelism: gradients of K and V back to the ranks that own the rows -------------------
+// After the two attention backward launches of a layer, rank s holds partial dK / dV for the key
+// prefixes of its two query chunks: call a covers rows [0, (s+1) n), call b rows [0, (2c-s) n) (zig-zag:
+// rank s owns sequence chunks s and 2c-1-s of n rows).  The backward kernels wrote them straight
+// into peer-visible buffers; this kernel lets every owner read, for each of its two chunks, the
+// partials of the peers whose prefix covers it, sum them in fp32 and store its bf16 dK / dV.
+struct CpDkvParams {
+  const bf16* ka[COLL_MAX_RANKS];     // rank s's dK of call a: [B, (s+1) n, row_elems]
+  const bf16* kb[COLL_MAX_RANKS];     // rank s's dK of call b: [B, (2c-s) n, row_elems]
+  const bf16* va[COLL_MAX_RANKS];
+  const bf16* vb[COLL_MAX_RANKS];
+  unsigned int* ready[COLL_MAX_RANKS];   // rank s's words [c]
+  bf16 *out_k, *out_v;                // [B, 2 n, row_elems]: chunk `me`, then chunk 2c-1-me
+  int B, n, row_elems, c, me;
+  unsigned int epoch;
+  unsigned long long wait_ns;
+};
+
+__global__ void __launch_bounds__(COLL_THREADS) cp_dkv_reduce_kernel(const CpDkvParams p) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  if (threadIdx.x < p.c) {
+    if (blockIdx.x == 0) {              // this kernel runs behind the launches that wrote this rank's partials
+      __threadfence_system();
+      lbcomm::st_release_sys(p.ready[threadIdx.x] + p.me, p.epoch);
+    }
+    if (!lbcomm::flag_wait_ge(p.ready[p.me] + threadIdx.x, p.epoch, p.wait_ns)) { s_fail = 1; coll_fail(30u); }
+  }
+  __syncthreads();
+  if (s_fail) return;
+  const int vpr = p.row_elems >> 3;
+  const long long total = (long long)p.B * 2 * p.n * vpr;
+  for (long long i = (long long)blockIdx.x * COLL_THREADS + threadIdx.x; i < total; i += (long long)gridDim.x * COLL_THREADS) {
+    const int v = (int)(i % vpr);
+    const long long br = i / vpr;
+    const int lr = (int)(br % (2 * p.n));              // local row: [chunk me | chunk 2c-1-me]
+    const int b = (int)(br / (2 * p.n));
+    const bool second = lr >= p.n;
+    const long long grow = second ? (long long)(2 * p.c - 1 - p.me) * p.n + (lr - p.n) : (long long)p.me * p.n + lr;
+    float ak[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, av[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < p.c; s++) {
+      float f[8];
+      const long long sk_a = (long long)(s + 1) * p.n, sk_b = (long long)(2 * p.c - s) * p.n;
+      if (grow < sk_a) {
+        const long long o = ((long long)b * sk_a + grow) * p.row_elems + v * 8;
+        unpack8(lbcomm::ld_nc_v4(p.ka[s] + o), f);
+#pragma unroll
+        for (int k = 0; k < 8; k++) ak[k] += f[k];
+        unpack8(lbcomm::ld_nc_v4(p.va[s] + o), f);
+#pragma unroll
+        for (int k = 0; k < 8; k++) av[k] += f[k];
+      }
+      if (grow < sk_b) {
+        const long long o = ((long long)b * sk_b + grow) * p.row_elems + v * 8;
+        unpack8(lbcomm::ld_nc_v4(p.kb[s] + o), f);
+#pragma unroll
+        for (int k = 0; k < 8; k++) ak[k] += f[k];
+        unpack8(lbcomm::ld_nc_v4(p.vb[s] + o), f);
+#pragma unroll
+        for (int k = 0; k < 8; k++) av[k] += f[k];
+      }
+    }
+    const long long oo = ((long long)b * 2 * p.n + lr) * p.row_elems + v * 8;
+    *reinterpret_cast<uint4*>(p.out_k + oo) = pack8(ak);
+    *reinterpret_cast<uint4*>(p.out_v + oo) = pack8(av);
+  }
+}
+
+// ---- Ulysses: sequence shards <-> head shards, layout change and RoPE inside the exchange -------------
+// mode 0 (before attention): src is the projection output [B * Sl, src_ld] of which columns
+//   [col0, col0 + H * d) are H heads; head h of local token (b, sl) is stored into rank h / hl's
+//   buffer [B, c * Sl, hl, d] at row me * Sl + sl (hl = H / c heads per rank), rotated on the way when
+//   cos / sin are given.  With rep > 1 (fewer KV heads than ranks) head h goes to ranks h * rep ..
+//   h * rep + rep - 1, one head per rank.
+// mode 1 (after attention): src [B, c * Sl, hl, d]; row (b, s) belongs to rank s / Sl, which receives
+//   it at heads me * hl .. me * hl + hl - 1 of a [B * Sl, dst_ld] matrix whose head columns start at
+//   dst_col0 (a plain [B, Sl, c * hl, d] tensor, or the q / k / v columns of a fused gradient).
+// Both directions are stores into peer-visible destinations (two buffers alternate by call); CTA b of
+// a rank signals CTA b of every peer when its stores are fenced and leaves once every peer's CTA b
+// has signalled, so at kernel end the whole destination is complete.
+struct UlyParams {
+  const bf16* src;
+  bf16* dst[COLL_MAX_RANKS];
+  unsigned int* flags[COLL_MAX_RANKS];     // [n][G]
+  const float *cosT, *sinT;                // [positions, d / 2] or null
+  const int* pos;                          // global position of local row sl, or null (= me * Sl + sl)
+  long long src_ld, col0;                  // mode 0: row stride and first column of the heads in src
+  long long dst_ld, dst_col0;              // mode 1: row stride and first column of the heads in dst
+  int mode, B, Sl, H, hl, d, rep, inverse;
+  int n, me, G;
+  unsigned int call;
+  unsigned long long wait_ns;
+};
+
+__global__ void __launch_bounds__(COLL_THREADS) ulysses_a2a_kernel(const UlyParams p) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  const int vph = p.d >> 3;                                   // 16-byte vectors per head
+  const int S = p.n * p.Sl;
+  const long long total = (p.mode == 0 ? (long long)p.B * p.Sl * p.H : (long long)p.B * S * p.hl) * vph;
+  const long long per = (total + p.G - 1) / p.G;
+  const long long lo = min(total, per * blockIdx.x), hi = min(total, per * (blockIdx.x + 1));
+  for (long long i = lo + threadIdx.x; i < hi; i += COLL_THREADS) {
+    const int v = (int)(i % vph);
+    long long t = i / vph;
+    if (p.mode == 0) {
+      const int h = (int)(t % p.H); t /= p.H;
+      const int sl = (int)(t % p.Sl);
+      const int b = (int)(t / p.Sl);
+      uint4 raw = *reinterpret_cast<const uint4*>(p.src + ((long long)b * p.Sl + sl) * p.src_ld + p.col0 + (long long)h * p.d + v * 8);
+      if (p.cosT) {
+        const int ps = p.pos ? p.pos[sl] : p.me * p.Sl + sl;
+        float f[8], o[8];
+        unpack8(raw, f);
+        const float4 c4 = *reinterpret_cast<const float4*>(p.cosT + (size_t)ps * (p.d >> 1) + v * 4);
+        float4 s4 = *reinterpret_cast<const float4*>(p.sinT + (size_t)ps * (p.d >> 1) + v * 4);
+        if (p.inverse) { s4.x = -s4.x; s4.y = -s4.y; s4.z = -s4.z; s4.w = -s4.w; }
+        o[0] = f[0] * c4.x - f[1] * s4.x; o[1] = f[0] * s4.x + f[1] * c4.x;
+        o[2] = f[2] * c4.y - f[3] * s4.y; o[3] = f[2] * s4.y + f[3] * c4.y;
+        o[4] = f[4] * c4.z - f[5] * s4.z; o[5] = f[4] * s4.z + f[5] * c4.z;
+        o[6] = f[6] * c4.w - f[7] * s4.w; o[7] = f[6] * s4.w + f[7] * c4.w;
+        raw = pack8(o);
+      }
+      const long long drow = (long long)b * S + (long long)p.me * p.Sl + sl;
+      if (p.rep <= 1) {
+        const int r = h / p.hl, hh = h - r * p.hl;
+        *reinterpret_cast<uint4*>(p.dst[r] + (drow * p.hl + hh) * p.d + v * 8) = raw;
+      } else {
+        for (int j = 0; j < p.rep; j++)
+          *reinterpret_cast<uint4*>(p.dst[h * p.rep + j] + drow * p.d + v * 8) = raw;
+      }
+    } else {
+      const int h = (int)(t % p.hl); t /= p.hl;
+      const int s = (int)(t % S);
+      const int b = (int)(t / S);
+      const uint4 raw = *reinterpret_cast<const uint4*>(p.src + (((long long)b * S + s) * p.hl + h) * p.d + v * 8);
+      const int r = s / p.Sl, sl = s - r * p.Sl;
+      *reinterpret_cast<uint4*>(p.dst[r] + ((long long)b * p.Sl + sl) * p.dst_ld + p.dst_col0 + ((long long)p.me * p.hl + h) * p.d + v * 8) = raw;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < p.n) {
+    __threadfence_system();
+    lbcomm::st_release_sys(p.flags[threadIdx.x] + ((size_t)p.me * p.G + blockIdx.x), p.call);
+    if (!lbcomm::flag_wait_ge(p.flags[p.me] + ((size_t)threadIdx.x * p.G + blockIdx.x), p.call, p.wait_ns)) coll_fail(40u);
+  }
+}
+
 int fill(CollParams& p, const void* in, void* out, void* const* stage_ptrs, void* const* flag_ptrs, long long half_bytes,
          long long chunk_elems, int elem_bytes, long long staged_elems, int n, int me, int G, unsigned int call) {
   if (n < 1 || n > COLL_MAX_RANKS || me < 0 || me >= n || G < 1 || chunk_elems <= 0) return LB_ERR_SHAPE;
@@ -285,6 +488,80 @@ extern "C" int lb_all_reduce_nvls(const void* in, void* out, void* const* stage_
   cudaStream_t s = (cudaStream_t)stream;
   if (elem_bytes == 4) all_reduce_nvls_kernel<float><<<G, COLL_THREADS, 0, s>>>(p);
   else all_reduce_nvls_kernel<bf16><<<G, COLL_THREADS, 0, s>>>(p);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}
+
+// Parameter gather of the sharded engine: src = this rank's bf16 shard, dst_ptrs[r] = rank r's
+// destination [n * shard_elems], arrive_ptrs[r] = rank r's arrival table [n][G] u32, free_words = this
+// rank's table [n] of released uses; `use` counts the gathers into this destination (1, 2, ...).
+extern "C" int lb_gather_into(const void* src, void* const* dst_ptrs, void* const* arrive_ptrs, const void* free_words,
+                              long long shard_elems, int n, int me, int G, unsigned int use, void* stream) {
+  if (n < 1 || n > COLL_MAX_RANKS || me < 0 || me >= n || G < 1 || shard_elems <= 0 || (shard_elems % 8) || use == 0)
+    return LB_ERR_SHAPE;
+  GatherParams p;
+  p.src = (const bf16*)src;
+  for (int r = 0; r < n; r++) { p.dst[r] = (bf16*)dst_ptrs[r]; p.arrive[r] = (unsigned int*)arrive_ptrs[r]; }
+  p.free_words = (const unsigned int*)free_words; p.shard_elems = shard_elems; p.n = n; p.me = me; p.G = G; p.use = use;
+  p.wait_ns = g_lb_flag_wait_ns;
+  gather_into_kernel<<<G, COLL_THREADS, 0, (cudaStream_t)stream>>>(p);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}
+
+// Tells every rank that this rank has finished use number `use` of a gather destination.
+extern "C" int lb_slot_release(void* const* free_ptrs, int n, int me, unsigned int use, void* stream) {
+  if (n < 1 || n > COLL_MAX_RANKS || me < 0 || me >= n) return LB_ERR_SHAPE;
+  ReleaseParams p;
+  for (int r = 0; r < n; r++) p.tab[r] = (unsigned int*)free_ptrs[r];
+  p.n = n; p.me = me; p.use = use;
+  slot_release_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(p);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}
+
+// Context-parallel dK / dV: ka / kb / va / vb: host arrays of c pointers (rank s's partials of its
+// call a / call b, see cp_dkv_reduce_kernel), ready_ptrs[s]: rank s's ready words [c]; epoch grows by
+// one per call on these words.  out_k / out_v: [B, 2 n, row_elems] bf16.
+extern "C" int lb_cp_dkv_reduce(void* const* ka, void* const* kb, void* const* va, void* const* vb, void* const* ready_ptrs,
+                                void* out_k, void* out_v, int B, int n, int row_elems, int c, int me, unsigned int epoch,
+                                void* stream) {
+  if (c < 1 || c > COLL_MAX_RANKS || me < 0 || me >= c || B <= 0 || n <= 0 || (row_elems % 8)) return LB_ERR_SHAPE;
+  CpDkvParams p;
+  for (int s = 0; s < c; s++) {
+    p.ka[s] = (const bf16*)ka[s]; p.kb[s] = (const bf16*)kb[s]; p.va[s] = (const bf16*)va[s]; p.vb[s] = (const bf16*)vb[s];
+    p.ready[s] = (unsigned int*)ready_ptrs[s];
+  }
+  p.out_k = (bf16*)out_k; p.out_v = (bf16*)out_v; p.B = B; p.n = n; p.row_elems = row_elems; p.c = c; p.me = me;
+  p.epoch = epoch; p.wait_ns = g_lb_flag_wait_ns;
+  const long long total = (long long)B * 2 * n * (row_elems / 8);
+  long long blocks = (total + COLL_THREADS - 1) / COLL_THREADS;
+  const long long cap = (long long)lb_num_sms() * 8;
+  if (blocks > cap) blocks = cap;
+  cp_dkv_reduce_kernel<<<(int)blocks, COLL_THREADS, 0, (cudaStream_t)stream>>>(p);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}
+
+// Ulysses exchange (see ulysses_a2a_kernel).  dst_ptrs[r] / flag_ptrs[r]: rank r's destination buffer
+// and flag table [n][G] u32 (zeroed once); call = 1, 2, ... per flag table.  cosT / sinT / pos may be null.
+extern "C" int lb_ulysses_a2a(int mode, const void* src, long long src_ld, long long col0, long long dst_ld,
+                              long long dst_col0, void* const* dst_ptrs,
+                              void* const* flag_ptrs, const void* cosT, const void* sinT, const void* pos, int inverse, int B,
+                              int Sl, int H, int hl, int d, int rep, int n, int me, int G, unsigned int call, void* stream) {
+  if (n < 1 || n > COLL_MAX_RANKS || me < 0 || me >= n || B <= 0 || Sl <= 0 || (d % 8) || G < 1) return LB_ERR_SHAPE;
+  if (mode == 0 && ((src_ld % 8) || (col0 % 8))) return LB_ERR_SHAPE;
+  if (mode == 1 && ((dst_ld % 8) || (dst_col0 % 8))) return LB_ERR_SHAPE;
+  if (mode == 0 && rep <= 1 && hl * n != H) return LB_ERR_SHAPE;
+  if (mode == 0 && rep > 1 && H * rep != n) return LB_ERR_SHAPE;
+  if ((cosT == nullptr) != (sinT == nullptr)) return LB_ERR_ARG;
+  UlyParams p;
+  p.src = (const bf16*)src;
+  for (int r = 0; r < n; r++) { p.dst[r] = (bf16*)dst_ptrs[r]; p.flags[r] = (unsigned int*)flag_ptrs[r]; }
+  p.cosT = (const float*)cosT; p.sinT = (const float*)sinT; p.pos = (const int*)pos; p.src_ld = src_ld; p.col0 = col0; p.dst_ld = dst_ld; p.dst_col0 = dst_col0;
+  p.mode = mode; p.B = B; p.Sl = Sl; p.H = H; p.hl = hl; p.d = d; p.rep = rep; p.inverse = inverse;
+  p.n = n; p.me = me; p.G = G; p.call = call; p.wait_ns = g_lb_flag_wait_ns;
+  ulysses_a2a_kernel<<<G, COLL_THREADS, 0, (cudaStream_t)stream>>>(p);
   LB_CHECK_LAUNCH();
   return LB_OK;
 }

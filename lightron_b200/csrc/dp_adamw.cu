@@ -9,6 +9,10 @@
 //   2. applies the decoupled-weight-decay Adam update to master / m / v (local fp32),
 //   3. stores the new bf16 parameters into every replica's parameter arena with 16-byte peer
 //      stores (the all-gather).
+// The same kernel serves the fully sharded engine (parallel/fsdp.py), one launch per block of the
+// model as its backward completes: there the reduced gradient can first be accumulated into an fp32
+// shard over several micro-batches (`acc`, with `do_update` only on the last), and the new bf16
+// parameters go to this rank's shard only (`push_all` = 0): the next forward gathers them.
 // The whole GPU takes part (hundreds of thousands of independent 16-byte loads in flight cover
 // the NVLink latency).  Two flag exchanges frame the kernel: "my gradients are complete" before any
 // peer load, and "my parameter pushes have landed" before the kernel may end, so that the next
@@ -32,6 +36,9 @@ struct DpParams {
   unsigned int epoch;
   float lr, b1, b2, eps, wd, bc1, bc2, gscale;
   unsigned long long wait_ns;      // limit of the two flag waits
+  float* acc;                      // fp32 gradient accumulator of the shard, or null
+  int do_update;                   // 0: only add the reduced gradient to acc
+  int push_all;                    // 1: new parameters go to every replica's arena, 0: to param[rank] only
 };
 
 using lbcomm::st_release_sys;
@@ -72,6 +79,20 @@ __global__ void __launch_bounds__(256) dp_adamw_kernel(const DpParams p) {
 #pragma unroll
       for (int k = 0; k < 8; k++) g[k] += f[k];
     }
+    if (p.acc) {
+      float a[8];
+      *reinterpret_cast<float4*>(a) = *reinterpret_cast<const float4*>(p.acc + i * 8);
+      *reinterpret_cast<float4*>(a + 4) = *reinterpret_cast<const float4*>(p.acc + i * 8 + 4);
+#pragma unroll
+      for (int k = 0; k < 8; k++) g[k] += a[k];
+      if (!p.do_update) {
+        *reinterpret_cast<float4*>(p.acc + i * 8) = *reinterpret_cast<const float4*>(g);
+        *reinterpret_cast<float4*>(p.acc + i * 8 + 4) = *reinterpret_cast<const float4*>(g + 4);
+        continue;
+      }
+      *reinterpret_cast<float4*>(p.acc + i * 8) = make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(p.acc + i * 8 + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     float w[8], mm[8], vv[8];
     *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(p.master + i * 8);
     *reinterpret_cast<float4*>(w + 4) = *reinterpret_cast<const float4*>(p.master + i * 8 + 4);
@@ -95,7 +116,11 @@ __global__ void __launch_bounds__(256) dp_adamw_kernel(const DpParams p) {
     *reinterpret_cast<float4*>(p.v + i * 8) = *reinterpret_cast<const float4*>(vv);
     *reinterpret_cast<float4*>(p.v + i * 8 + 4) = *reinterpret_cast<const float4*>(vv + 4);
     const uint4 packed = pack8(w);
-    for (int r = 0; r < p.n; r++) *reinterpret_cast<uint4*>(p.param[r] + e) = packed;
+    if (p.push_all) {
+      for (int r = 0; r < p.n; r++) *reinterpret_cast<uint4*>(p.param[r] + e) = packed;
+    } else {
+      *reinterpret_cast<uint4*>(p.param[p.rank] + e) = packed;
+    }
   }
 
   // ---- second flag exchange: my pushes have landed everywhere; leave only when everybody's have ----
@@ -127,10 +152,11 @@ extern "C" int lb_dp_status(void* out) {
 // flag words (16 x u32 per rank) and block_counter (1 x u32, local) are zeroed once; `epoch` and
 // `grid_blocks` must be the same on every call (epoch grows by one per call).  shard_start and
 // shard_len are in elements, multiples of 8.
-extern "C" int lb_dp_adamw(void* const* grad_ptrs, void* const* param_ptrs, void* const* flag_ptrs, void* block_counter,
+static int dp_adamw_launch(void* const* grad_ptrs, void* const* param_ptrs, void* const* flag_ptrs, void* block_counter,
                            void* master, void* m, void* v, long long shard_start, long long shard_len, int n, int rank,
                            unsigned int epoch, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
-                           float gscale, int grid_blocks, void* stream) {
+                           float gscale, int grid_blocks, void* acc, int do_update, int push_all, void* stream) {
+  if (!do_update && acc == nullptr) return LB_ERR_ARG;
   if (n < 1 || n > MAX_RANKS || shard_len <= 0 || (shard_len % 8) || (shard_start % 8) || grid_blocks < 1) return LB_ERR_SHAPE;
   DpParams p;
   for (int r = 0; r < n; r++) {
@@ -142,8 +168,29 @@ extern "C" int lb_dp_adamw(void* const* grad_ptrs, void* const* param_ptrs, void
   p.master = (float*)master; p.m = (float*)m; p.v = (float*)v;
   p.shard_start = shard_start; p.shard_len = shard_len; p.n = n; p.rank = rank; p.epoch = epoch;
   p.wait_ns = g_lb_flag_wait_ns;
+  p.acc = (float*)acc; p.do_update = do_update; p.push_all = push_all;
   p.lr = lr; p.b1 = b1; p.b2 = b2; p.eps = eps; p.wd = wd; p.bc1 = bc1; p.bc2 = bc2; p.gscale = gscale;
   dp_adamw_kernel<<<grid_blocks, 256, 0, (cudaStream_t)stream>>>(p);
   LB_CHECK_LAUNCH();
   return LB_OK;
+}
+
+extern "C" int lb_dp_adamw(void* const* grad_ptrs, void* const* param_ptrs, void* const* flag_ptrs, void* block_counter,
+                           void* master, void* m, void* v, long long shard_start, long long shard_len, int n, int rank,
+                           unsigned int epoch, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                           float gscale, int grid_blocks, void* stream) {
+  return dp_adamw_launch(grad_ptrs, param_ptrs, flag_ptrs, block_counter, master, m, v, shard_start, shard_len, n, rank,
+                         epoch, lr, b1, b2, eps, wd, bc1, bc2, gscale, grid_blocks, nullptr, 1, 1, stream);
+}
+
+// The sharded engine's form: `acc` (fp32 [shard_len], zeroed once) collects the reduced gradient of
+// micro-batches launched with do_update = 0; the launch with do_update = 1 adds its own reduced
+// gradient, steps AdamW and clears acc.  push_all = 0 stores the new bf16 parameters at
+// param_ptrs[rank] + shard_start only (pass a pointer such that this lands in the shard buffer).
+extern "C" int lb_fsdp_rs_adamw(void* const* grad_ptrs, void* const* param_ptrs, void* const* flag_ptrs, void* block_counter,
+                                void* master, void* m, void* v, void* acc, long long shard_start, long long shard_len, int n,
+                                int rank, unsigned int epoch, float lr, float b1, float b2, float eps, float wd, float bc1,
+                                float bc2, float gscale, int grid_blocks, int do_update, int push_all, void* stream) {
+  return dp_adamw_launch(grad_ptrs, param_ptrs, flag_ptrs, block_counter, master, m, v, shard_start, shard_len, n, rank,
+                         epoch, lr, b1, b2, eps, wd, bc1, bc2, gscale, grid_blocks, acc, do_update, push_all, stream);
 }

@@ -46,6 +46,7 @@ using namespace bw;
 // destination's flag word.  The attention CTAs gate every 128-key block on its flag, so the
 // exchange overlaps the softmax / MMA work on blocks that have already arrived.
 constexpr int FA_MAX_RANKS = 8;
+constexpr int FA_FWD_THREADS = 384;
 struct FaPush {
   int n_mov, n_ranks, rank, chunk_rows, row_elems;   // row_elems = hkv * d
   const bf16 *k_src, *v_src;                         // this rank's [B, 2*chunk_rows, hkv, d], token strides below
@@ -94,7 +95,7 @@ struct FaCfg {
 };
 
 template <int D>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(FA_FWD_THREADS, 1)
 fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                  const __grid_constant__ CUtensorMap tv, const FaFwdParams p, const FaPush push) {
   using C = FaCfg<D>;
@@ -482,7 +483,7 @@ int launch_fa_fwd(const void* q, const void* k, const void* v, FaFwdParams p, co
   p.wait_ns = g_lb_flag_wait_ns;
   const long long grid = (long long)push.n_mov + (long long)p.tiles_x * p.hq * p.B;
   if (grid > 2147483647LL) return LB_ERR_SHAPE;
-  fa_fwd_tc_kernel<D><<<(unsigned)grid, 384, C::SMEM, s>>>(tq, tk, tv, p, push);
+  fa_fwd_tc_kernel<D><<<(unsigned)grid, FA_FWD_THREADS, C::SMEM, s>>>(tq, tk, tv, p, push);
   LB_CHECK_LAUNCH();
   return LB_OK;
 }
@@ -526,6 +527,10 @@ extern "C" int lb_flash_fwd_tc(const void* q, const void* k, const void* v, void
     default: return LB_ERR_SHAPE;
   }
 }
+
+// Warps per CTA of the forward kernel: every mover warp adds 1 to a key block's arrival word for K
+// and 1 for V, so a block is complete at (calls so far) * 2 * this.
+extern "C" int lb_flash_fwd_cp_mover_warps() { return FA_FWD_THREADS / 32; }
 
 // Context-parallel forward: attention of q [B, Sq, hq, d] over the first Sk keys of the gather
 // buffers kg / vg ([B, S_full, hkv*d] contiguous, this rank's peer-visible buffers), each 128-key

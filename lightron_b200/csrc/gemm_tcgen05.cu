@@ -361,6 +361,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // these rows, which they produce FIRST, have normally landed in the receive area long ago):
         // wait for them, add them to the accumulator and store the finished bf16 rows.  No trip
         // through the receive area for the own partial, no second kernel for the sum.
+        if (rs_npend > 0) {
+          // the counts of the tiles already sent must leave before this rank starts waiting for its
+          // peers: they are waiting for exactly those counts
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0)
+            for (int i = 0; i < rs_npend; i++) red_release_sys_add(rs_pend[i], 1u);
+          rs_npend = 0;
+        }
         bool arrived = true;
         for (int s = 0; s < cp.n_ranks; s++)
           if (s != cp.rank && !flag_wait_ge(cp.rs_flags[cp.rank] + s * cp.blocks_per_rank + lb, cp.rs_target, cp.wait_ns, 21u))
@@ -567,6 +576,30 @@ int init_sms() {
   }
   return g_num_sms;
 }
+// raises `count` consecutive arrival counters by `inc` (after a copy-engine transfer has landed)
+__global__ void ag_flag_bump_kernel(unsigned int* flags, int count, unsigned int inc) {
+  for (int i = threadIdx.x; i < count; i += blockDim.x) {
+    __threadfence_system();
+    red_release_sys_add(flags + i, inc);
+  }
+}
+
+// per-device side stream and events of the copy-engine all-gather
+struct CeState { cudaStream_t stream; cudaEvent_t ready, done; };
+CeState* ce_state() {
+  static CeState st[64];
+  static bool made[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!made[dev]) {
+    if (cudaStreamCreateWithFlags(&st[dev].stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&st[dev].ready, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&st[dev].done, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    made[dev] = true;
+  }
+  return &st[dev];
+}
+
 void bind_ctx() {
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) {
@@ -580,7 +613,9 @@ void bind_ctx() {
 // x_local [M/n, K] (row stride ld_x), rows [rank*M/n, ...).  gather_ptrs[r] = rank r's gather buffer
 // [M,K] contiguous (peer pointers for r != rank); after the kernel gather_ptrs[rank] holds the whole
 // gathered operand.  flag_ptrs[r] = rank r's block counters [M/128] (zeroed once); ag_target =
-// (number of calls that used these counters, this one included) * 6.
+// (number of calls that used these counters, this one included) * 6.  n_comm > 0: that many mover
+// CTAs inside the kernel push the rows; n_comm < 0: copy-engine transfers on a side stream bring
+// them instead and every SM runs GEMM tiles.
 // M must be a multiple of 128 * n_ranks.  gather_ptrs / flag_ptrs are host arrays of n_ranks pointers.
 extern "C" int lb_gemm_ag(const void* B, void* C, int M, int N, int K, long long ldb, long long ldc, int b_mn,
                           int n_ranks, int rank, const void* x_local, long long ld_x, void* const* gather_ptrs,
@@ -606,15 +641,48 @@ extern "C" int lb_gemm_ag(const void* B, void* C, int M, int N, int K, long long
   CommParams cp;
   memset(&cp, 0, sizeof(cp));
   cp.n_ranks = n_ranks; cp.rank = rank; cp.rows_per_rank = M / n_ranks; cp.blocks_per_rank = cp.rows_per_rank / BM;
-  if (n_comm < 1) n_comm = 1;
+  const bool copy_engine = n_comm < 0;          // rows travel by copy-engine transfers issued here, not by mover CTAs
+  if (copy_engine) n_comm = 0;
+  else if (n_comm < 1) n_comm = 1;
   if (n_comm > sms / 2) n_comm = sms / 2;
   cp.n_comm = n_comm; cp.ag_target = ag_target; cp.wait_ns = g_lb_flag_wait_ns;
   cp.x_local = (const bf16*)x_local; cp.ld_x = ld_x;
   for (int r = 0; r < n_ranks; r++) { cp.gather[r] = (bf16*)gather_ptrs[r]; cp.ag_flags[r] = (unsigned int*)flag_ptrs[r]; }
+  CeState* ce = nullptr;
+  if (copy_engine) {
+    // Side stream: one peer copy per destination and quarter of this rank's rows (the copy engines
+    // reach about twice the NVLink rate that SM-issued stores were measured at here), each followed by
+    // a few-thread kernel that raises the arrival counters of the copied 128-row blocks by the same
+    // amount the mover warps would.  The GEMM kernel below starts at once on all SMs and consumes the
+    // blocks as their counters arrive; the calling stream is made to wait for the copies afterwards,
+    // so x_local may be reused by whatever is enqueued next.
+    ce = ce_state();
+    if (ce == nullptr) return LB_ERR_LAUNCH;
+    cudaStream_t main = (cudaStream_t)stream;
+    cudaEventRecord(ce->ready, main);
+    cudaStreamWaitEvent(ce->stream, ce->ready, 0);
+    const int bpr = cp.blocks_per_rank;
+    const int parts = bpr >= 4 ? 4 : 1;
+    const bf16* xl = (const bf16*)x_local;
+    for (int pt = 0; pt < parts; pt++) {
+      const int b0 = (int)((long long)bpr * pt / parts), b1 = (int)((long long)bpr * (pt + 1) / parts);
+      const size_t r0 = (size_t)b0 * BM, nrows = (size_t)(b1 - b0) * BM;
+      for (int j = 1; j <= n_ranks; j++) {                      // peers first, the local copy last
+        const int dst = (rank + j) % n_ranks;
+        bf16* d = cp.gather[dst] + ((size_t)rank * cp.rows_per_rank + r0) * K;
+        cudaMemcpy2DAsync(d, (size_t)K * 2, xl + r0 * ld_x, (size_t)ld_x * 2, (size_t)K * 2, nrows, cudaMemcpyDeviceToDevice,
+                          ce->stream);
+        if (dst != rank)
+          ag_flag_bump_kernel<<<1, 128, 0, ce->stream>>>(cp.ag_flags[dst] + rank * bpr + b0, b1 - b0, (unsigned)MOVER_WARPS);
+      }
+    }
+    cudaEventRecord(ce->done, ce->stream);
+  }
   int n_gemm = sms - n_comm;
   if (n_gemm > p.num_tiles) n_gemm = p.num_tiles;
   gemm_bf16_kernel<1><<<n_comm + n_gemm, NUM_THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(ta, tb, town, (bf16*)C, p, cp);
   LB_CHECK_LAUNCH();
+  if (ce) cudaStreamWaitEvent((cudaStream_t)stream, ce->done, 0);
   return LB_OK;
 }
 

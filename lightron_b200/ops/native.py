@@ -67,6 +67,11 @@ _SIGNATURES = {
     "lb_swiglu_fwd_dev": [_P, _P, _I, _I, _L, _P, _P],
     "lb_swiglu_bwd_dev": [_P, _P, _P, _I, _I, _L, _P, _P],
     "lb_coll_status": [_P],
+    "lb_ulysses_a2a": [_I, _P, _L, _L, _L, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, ctypes.c_uint, _P],
+    "lb_cp_dkv_reduce": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, ctypes.c_uint, _P],
+    "lb_gather_into": [_P, _P, _P, _P, _L, _I, _I, _I, ctypes.c_uint, _P],
+    "lb_slot_release": [_P, _I, _I, ctypes.c_uint, _P],
+    "lb_fsdp_rs_adamw": [_P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _I, _I, ctypes.c_uint, _F, _F, _F, _F, _F, _F, _F, _F, _I, _I, _I, _P],
     "lb_collective": [_I, _P, _P, _P, _P, _L, _L, _I, _I, _I, _I, ctypes.c_uint, _P],
     "lb_all_reduce_nvls": [_P, _P, _P, _P, _P, _L, _L, _I, _I, _I, _I, ctypes.c_uint, _P],
     "lb_dp_status": [_P],
@@ -74,6 +79,7 @@ _SIGNATURES = {
     "lb_flash_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _P],
     "lb_flash_fwd_tc": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _F, _I, _P],
     "lb_flash_status": [_P],
+    "lb_flash_fwd_cp_mover_warps": [],
     "lb_flash_fwd_cp": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _L, _F, _I, _P, ctypes.c_uint, _I, _P, _P,
                         _L, _L, _I, _I, _P, _P, _P, _I, _P],
     "lb_flash_bwd_cp": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,

@@ -225,6 +225,11 @@ def context_parallel_attention(qkv, cos, sin, positions, B, S, hq, hkv, d, group
     ``positions`` are the global positions of the local rows (zig-zag for ring, contiguous for
     Ulysses); RoPE is applied locally before any exchange."""
     T = B * S
+    if mode == "ulysses" and comm.group_size(group) > 1:
+        from . import ulysses_fused
+        if ulysses_fused.fused_ok(qkv, group, hq, hkv, d):
+            # exchange, layout change and RoPE in one kernel per direction (peer stores over NVLink)
+            return ulysses_fused.ulysses_attention_qkv(qkv, cos, sin, positions, B, S, hq, hkv, d, group)
     q, k, v = qkv.view(T, -1).split([hq * d, hkv * d, hkv * d], dim=-1)
     q = OF.rope(q.reshape(B, S, hq, d), cos, sin, positions)
     k = OF.rope(k.reshape(B, S, hkv, d), cos, sin, positions)

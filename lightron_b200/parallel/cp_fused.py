@@ -8,8 +8,9 @@ counters arrive (``lb_flash_fwd_cp``).  Each query chunk then needs exactly one 
 over a key prefix: chunk r over keys [0, (r+1)n), chunk 2c-1-r over keys [0, (2c-r)n); both are
 plain bottom-right-aligned causal problems, so there is no partial-result merging at all.
 GQA keeps the exchanged bytes small (only KV heads move) and 180 GB of HBM makes the gathered
-prefix affordable as the tensor saved for backward.  Backward runs the two attention backwards
-and reduce-scatters dK/dV to the owners of the chunks.
+prefix affordable as the tensor saved for backward.  Backward runs the two attention backwards, which
+store their dK / dV partials into peer-visible buffers, and one kernel (``lb_cp_dkv_reduce``) in which
+every owner reads and sums the partials that cover its chunks.
 
 The reference has no counterpart (its ring attention is a forward-only non-causal demo,
 parallel/communication/ring_attention.py:10-119); the north-star asks for the exchange to be
@@ -30,7 +31,6 @@ from ..ops import native, reference as ref
 from . import comm
 
 _MOVER_CTAS = 16
-_WARPS = 10                      # warps per mover CTA (320 threads): each adds 1 per K and per V block
 
 
 class _Workspace:
@@ -41,8 +41,13 @@ class _Workspace:
         self.fpb = S // 128
         self.flag_bytes = (2 * B * self.fpb * 4 + 255) // 256 * 256
         self.buf_bytes = (B * S * row_elems * 2 + 255) // 256 * 256
-        total = self.flag_bytes + 4 * self.buf_bytes            # 2 slots x (K, V)
+        # 2 slots x (K, V) for the forward exchange, then 2 parities x (dK a, dK b, dV a, dV b) partials of
+        # the backward, then the ready words of the dK / dV reduction
+        self.grad_off0 = self.flag_bytes + 4 * self.buf_bytes
+        self.ready_off = self.grad_off0 + 8 * self.buf_bytes
+        total = self.ready_off + 256
         self.buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
+        self.buf[self.ready_off:].zero_()
         self.buf[: self.flag_bytes].zero_()
         hdl = symm_mem.rendezvous(self.buf, group=group)
         off = int(getattr(hdl, "offset", 0))
@@ -51,6 +56,7 @@ class _Workspace:
         dist.barrier(group=group)
         self.calls = 0
         self.uses = [0, 0]
+        self.bwd_calls = 0
 
     def arr(self, off: int):
         a = (ctypes.c_void_p * self.n)()
@@ -66,6 +72,10 @@ class _Workspace:
 
     def v_off(self, slot: int) -> int:
         return self.flag_bytes + (2 * slot + 1) * self.buf_bytes
+
+    def grad_off(self, parity: int, which: int) -> int:
+        """which: 0 dK of call a, 1 dK of call b, 2 dV of call a, 3 dV of call b."""
+        return self.grad_off0 + (4 * parity + which) * self.buf_bytes
 
     def view(self, off: int, B: int, S: int, hkv: int, d: int) -> torch.Tensor:
         return self.buf[off:off + B * S * hkv * d * 2].view(torch.bfloat16).view(B, S, hkv, d)
@@ -92,13 +102,15 @@ def fused_ok(q: torch.Tensor, group) -> bool:
     return symm.supported(group) and d in (64, 128) and Sl % 256 == 0
 
 
-def _bwd_call(q, kbuf, vbuf, Sk, kv_brows, o, lse, do, scale):
-    """Attention backward of q [B,n,hq,d] over the first Sk keys of every batch of kbuf/vbuf."""
+def _bwd_call(q, kbuf, vbuf, Sk, kv_brows, o, lse, do, scale, dk=None, dv=None):
+    """Attention backward of q [B,n,hq,d] over the first Sk keys of every batch of kbuf/vbuf.
+    dk / dv [B, Sk, hkv, d] may be views of peer-visible memory."""
     B, Sq, hq, d = q.shape
     hkv = kbuf.shape[2]
     dq = torch.empty_like(q)
-    dk = torch.empty(B, Sk, hkv, d, dtype=q.dtype, device=q.device)
-    dv = torch.empty_like(dk)
+    if dk is None:
+        dk = torch.empty(B, Sk, hkv, d, dtype=q.dtype, device=q.device)
+        dv = torch.empty_like(dk)
     delta = torch.empty(B, hq, Sq, dtype=torch.float32, device=q.device)
     dq_acc = torch.zeros(B * hq * ((Sq + 127) // 128) * 128 * d, dtype=torch.float32, device=q.device)
     native.call("lb_flash_bwd_cp", q.data_ptr(), kbuf.data_ptr(), vbuf.data_ptr(), o.data_ptr(), do.data_ptr(),
@@ -120,7 +132,7 @@ class _AllGatherKVAttention(torch.autograd.Function):
         slot = ws.calls % 2
         ws.calls += 1
         ws.uses[slot] += 1
-        target = ws.uses[slot] * 2 * _WARPS
+        target = ws.uses[slot] * 2 * native.require().lb_flash_fwd_cp_mover_warps()   # every mover warp counts K and V
         k, v = k.contiguous(), v.contiguous()
         qa, qb = q[:, :n].contiguous(), q[:, n:].contiguous()
         sk_a, sk_b = (r + 1) * n, (2 * c - r) * n
@@ -149,20 +161,26 @@ class _AllGatherKVAttention(torch.autograd.Function):
         group, scale, c, r, n, sk_a, sk_b = ctx.meta
         B, _, hkv, d = kk.shape
         do_a, do_b = do[:, :n].contiguous(), do[:, n:].contiguous()
-        dqa, dka, dva = _bwd_call(qa, kk, vk, sk_a, sk_b, oa, la, do_a, scale)
-        dqb, dkb, dvb = _bwd_call(qb, kk, vk, sk_b, sk_b, ob, lb, do_b, scale)
-        S = 2 * c * n
-        dkv = torch.zeros(2, B, S, hkv, d, dtype=torch.float32, device=do.device)
-        dkv[0, :, :sk_b] += dkb.float()
-        dkv[1, :, :sk_b] += dvb.float()
-        dkv[0, :, :sk_a] += dka.float()
-        dkv[1, :, :sk_a] += dva.float()
-        # rows of the owner j are chunks j and 2c-1-j: bring them together, then reduce-scatter
-        idx = torch.tensor([x for j in range(c) for x in (j, 2 * c - 1 - j)], device=do.device)
-        by_owner = dkv.view(2, B, 2 * c, n, hkv, d).index_select(2, idx).view(2, B, c, 2 * n, hkv, d)
-        by_owner = by_owner.permute(2, 0, 1, 3, 4, 5).contiguous()                 # [c, 2, B, 2n, hkv, d]
-        mine = comm.reduce_scatter_rows(by_owner.view(c, -1), group).view(2, B, 2 * n, hkv, d)
-        return torch.cat((dqa, dqb), dim=1), mine[0].to(do.dtype), mine[1].to(do.dtype), None, None
+        # The backward kernels store their dK / dV partials straight into peer-visible buffers; one
+        # kernel then lets every owner read the partials that cover its two chunks, sum them in fp32
+        # and keep its rows (no full-sequence fp32 buffer, no library reduce-scatter).  Two sets of
+        # buffers alternate: a rank can reach the layer after next only after every peer has finished
+        # reading this layer's partials.
+        ws = _WS[id(group)]
+        par = ws.bwd_calls % 2
+        ws.bwd_calls += 1
+        views = []
+        for which, sk in ((0, sk_a), (1, sk_b), (2, sk_a), (3, sk_b)):
+            off = ws.grad_off(par, which)
+            views.append(ws.buf[off:off + B * sk * hkv * d * 2].view(torch.bfloat16).view(B, sk, hkv, d))
+        dqa, _, _ = _bwd_call(qa, kk, vk, sk_a, sk_b, oa, la, do_a, scale, views[0], views[2])
+        dqb, _, _ = _bwd_call(qb, kk, vk, sk_b, sk_b, ob, lb, do_b, scale, views[1], views[3])
+        dk = torch.empty(B, 2 * n, hkv, d, dtype=do.dtype, device=do.device)
+        dv = torch.empty_like(dk)
+        native.call("lb_cp_dkv_reduce", ws.arr(ws.grad_off(par, 0)), ws.arr(ws.grad_off(par, 1)), ws.arr(ws.grad_off(par, 2)),
+                    ws.arr(ws.grad_off(par, 3)), ws.arr(ws.ready_off), dk.data_ptr(), dv.data_ptr(), B, n, hkv * d, c, r,
+                    ws.bwd_calls, native.stream_ptr())
+        return torch.cat((dqa, dqb), dim=1), dk, dv, None, None
 
 
 def _oracle_path(q, k, v, group, scale, positions):

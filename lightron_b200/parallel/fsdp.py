@@ -220,3 +220,44 @@ def apply_fsdp1(model: nn.Module, strategy: str = "full", activation_checkpointi
         raise ValueError(f"unknown FSDP strategy {strategy}")
     return apply_fsdp2(model, ctx=ctx, param_dtype=param_dtype, reshard_after_forward=(strategy != "grad_op"),
                        activation_checkpointing=activation_checkpointing)
+
+
+class FSDPOptimizer:
+    """The trainer-facing optimizer of a model wrapped by :func:`apply_fsdp2` (library collectives,
+    ``torch.optim.AdamW`` on the fp32 master shards): the same small interface as
+    ``optim.DistributedAdamW`` and ``fsdp_native.NativeFSDP``."""
+
+    def __init__(self, model: nn.Module, lr: float, weight_decay: float, betas=(0.9, 0.999), eps: float = 1e-8):
+        self.model, self.state = model, model._fsdp
+        self.opt = self.state.make_optimizer(lr=lr, weight_decay=weight_decay, betas=betas, eps=eps)
+        self.step_count = 0
+        self.shard_numel = sum(u.shard_len for u in self.state.units)
+
+    def set_requires_gradient_sync(self, flag: bool) -> None:
+        self.state.set_requires_gradient_sync(flag)
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        self.opt.zero_grad(set_to_none=True)
+
+    def finish_grad_sync(self) -> None:
+        pass
+
+    def step(self) -> None:
+        self.opt.step()
+        self.step_count += 1
+
+    def refresh_master_from_params(self) -> None:
+        pass
+
+    def state_dict(self):
+        return {"step": self.step_count, "torch": self.opt.state_dict(), "shard_numel": self.shard_numel,
+                "masters": [u.shard.detach().cpu() for u in self.state.units]}
+
+    def load_state_dict(self, sd) -> None:
+        assert sd["shard_numel"] == self.shard_numel, "optimizer shard layout differs"
+        self.step_count = int(sd["step"])
+        with torch.no_grad():
+            for u, m in zip(self.state.units, sd["masters"]):
+                u.shard.copy_(m)
+        self.opt.load_state_dict(sd["torch"])
+        self.state.refresh()

@@ -42,6 +42,9 @@ _MAX_BLOCKS = 4096             # 128-row blocks per gather buffer (tokens <= 524
 _MAX_BPR = 1024
 _MOVER_WARPS = 6               # warps per mover CTA: each adds 1 to a block counter
 N_COMM_CTAS = int(os.environ.get("LIGHTRON_AG_CTAS", "0"))     # 0 = choose per call from the GEMM size
+# how the gathered rows travel: "sm" = mover CTAs inside the GEMM kernel (peer stores), "ce" = copy-engine
+# transfers issued next to the kernel (about twice the link rate; the kernel consumes blocks as they land)
+AG_TRANSPORT = os.environ.get("LIGHTRON_AG_TRANSPORT", "sm")
 DEFAULT_KEEP_SLOTS = 8
 
 
@@ -182,7 +185,9 @@ def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, k
     # CTAs that push rows instead of doing MMAs: a short GEMM needs the gather done quickly (more
     # movers), a long one hides it behind the math anyway (fewer movers, more tensor-core SMs).
     n_comm = N_COMM_CTAS
-    if n_comm <= 0:
+    if AG_TRANSPORT == "ce":
+        n_comm = -1                 # copy-engine transfers on a side stream, all SMs on the GEMM
+    elif n_comm <= 0:
         flops = 2.0 * M * N * K
         n_comm = 32 if flops < 1.2e11 else (16 if flops < 6e11 else 8)
     gathers = ws.ptr_array(ws.gather_off(slot))

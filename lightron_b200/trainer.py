@@ -78,8 +78,7 @@ class Trainer:
         self.net = net
         init_weights(net, seed=t.seed)
         net.train()
-        self.optimizer = DistributedAdamW(net, lr=t.learning_rate, weight_decay=t.weight_decay, betas=t.betas,
-                                          eps=t.eps, ctx=ctx, grad_clip=t.grad_clip)
+        self.optimizer = self._build_engine(net)
         cp_mode = "zigzag" if (d.cp_size > 1 and d.cp_mode in ("ring", "allgather")) else "contiguous"
         self.dataloader = MicroBatchDataLoader(
             micro_batch_size=t.micro_batch_size, seq_length=t.seq_length, dataset_name=cfg.dataset.name,
@@ -122,6 +121,30 @@ class Trainer:
         if t.resume:
             meta = ckpt.load(t.resume, self.model, self.optimizer, self.dataloader, ctx)
             self.step, self.tokens_seen = meta["trained_steps"], meta["trained_tokens"]
+
+    def _build_engine(self, net):
+        """Data-parallel engine.  Default: replicated bf16 parameters, optimizer state sharded over the
+        replicas (``DistributedAdamW``).  ``distributed.fsdp``: parameters, gradients and optimizer
+        state sharded per transformer block (the reference wires ``apply_fsdp2`` whenever dp > 1,
+        trainer.py:198-203): the peer-memory engine when the layout allows it, else the
+        library-collective one."""
+        d, t, ctx = self.cfg.distributed, self.cfg.training, self.ctx
+        if d.fsdp and ctx.grad_replicas > 1:
+            from .parallel import fsdp as fsdp_lib, fsdp_native
+            why_not = fsdp_native.supported(net, ctx, self.dtype, t.grad_clip)
+            if why_not is None:
+                self.engine = "fsdp (peer-memory kernels)"
+                return fsdp_native.NativeFSDP(net, ctx, lr=t.learning_rate, weight_decay=t.weight_decay, betas=t.betas, eps=t.eps)
+            if d.pp_size == 1 and not any(getattr(p, "is_expert", False) for p in net.parameters()):
+                self.engine = f"fsdp (library collectives: {why_not})"
+                fsdp_lib.apply_fsdp2(net, ctx=ctx, param_dtype=self.dtype)
+                return fsdp_lib.FSDPOptimizer(net, lr=t.learning_rate, weight_decay=t.weight_decay, betas=t.betas, eps=t.eps)
+            if ctx.rank == 0:
+                print(f"[lightron] distributed.fsdp ignored for this layout ({why_not}); using the sharded-optimizer engine",
+                      flush=True)
+        self.engine = "sharded optimizer (replicated bf16 parameters)"
+        return DistributedAdamW(net, lr=t.learning_rate, weight_decay=t.weight_decay, betas=t.betas, eps=t.eps, ctx=ctx,
+                                grad_clip=t.grad_clip)
 
     # ------------------------------------------------------------------------------------------
     def train_step(self) -> torch.Tensor:
@@ -173,7 +196,7 @@ class Trainer:
         log_f = open(t.jsonl_log, "a") if (t.jsonl_log and is_log) else None
         if ctx.rank == 0:
             n = sum(p.numel() for p in self.net.parameters())
-            print(f"Model initialized. Local parameters: {n / 1e9:.3f}B | {ctx.describe()}", flush=True)
+            print(f"Model initialized. Local parameters: {n / 1e9:.3f}B | {ctx.describe()} | engine: {self.engine}", flush=True)
             print("\n=== Start Training ===", flush=True)
         start = time.time()
         first_step, tokens0 = self.step, self.tokens_seen

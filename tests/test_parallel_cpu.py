@@ -169,3 +169,9 @@ def test_ep2_expert_gradients_match_single_process():
             assert torch.allclose(g, w, rtol=1e-3, atol=1e-7), f"{name}: norm ratio {float(g.norm() / w.norm()):.4f}"
             seen += 1
     assert seen == len(want)
+
+
+def test_dp2_fsdp_flag_selects_sharded_parameter_engine():
+    """``distributed.fsdp: true`` on CPU ranks: per-block sharded parameters through library
+    collectives, same losses as the single process."""
+    _check(_cfg({"dp_size": 2, "fsdp": True}), 2, 3)

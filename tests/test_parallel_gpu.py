@@ -130,6 +130,16 @@ def test_ep2_moe(tmp_path):
            model_kw={"moe_num_experts": 4, "moe_topk": 2, "moe_layer_freq": 2, "moe_aux_loss_coef": 0.0})
 
 
+def test_dp2_fsdp_peer_memory_engine(tmp_path):
+    """distributed.fsdp on 2 GPUs: parameters sharded per block, gathers and the fused
+    reduce-scatter + AdamW kernel over peer memory; parameters after 3 steps vs one GPU."""
+    _check(tmp_path, 2, {"dp_size": 2, "fsdp": True})
+
+
+def test_dp2_fsdp_gradient_accumulation(tmp_path):
+    _check(tmp_path, 2, {"dp_size": 2, "fsdp": True}, {"gradient_accumulation_steps": 2, "micro_batch_size": 2})
+
+
 def test_tp2_dp2_fused(tmp_path):
     _check(tmp_path, 4, {"tp_size": 2, "dp_size": 2, "sequence_parallel": True})
 
