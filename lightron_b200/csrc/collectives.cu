@@ -425,6 +425,109 @@ __global__ void __launch_bounds__(COLL_THREADS) ulysses_a2a_kernel(const UlyPara
   }
 }
 
+// ---- vocab-parallel embedding by peer stores --------------------------------------------------------
+// Rank r holds the rows of the table for vocab ids [v0, v1).  The library form (reference
+// parallel/parallel_tp.py:131-143) looks up a mostly-zero [T, H] partial on every rank and
+// all-reduces (or reduce-scatters) it.  Here every row travels exactly once: the rank that owns a
+// token's id stores the row straight into the staging buffer of the rank that needs it (under
+// sequence parallelism the owner of row t / rows_per_rank; otherwise every rank), and the receiver
+// copies its finished rows out.  CTA b of every rank handles the same slice of the tokens, so CTA b only
+// ever waits for CTA b of its peers.  Backward (sequence parallel): every rank publishes its
+// gradient rows in its staging buffer and adds, for the tokens whose ids it owns, the rows it reads
+// from their owners into its table gradient.
+struct EmbParams {
+  const long long* tok;                    // [T] token ids (the same on every rank)
+  const bf16* w;                           // forward: local table rows [v1 - v0, H]
+  bf16* out;                               // forward: [rows kept, H];  backward: table gradient [v1 - v0, H]
+  const bf16* dy;                          // backward: this rank's gradient rows [rpr, H]
+  bf16* stage[COLL_MAX_RANKS];
+  unsigned int* flags[COLL_MAX_RANKS];     // [n][G]
+  int T, H, v0, v1, n, me, G, sp, rpr;     // rpr: rows per rank under sp
+  unsigned int call;
+  unsigned long long wait_ns;
+};
+
+__device__ __forceinline__ bool emb_exchange(const EmbParams& p, int* s_fail, unsigned where) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < p.n) {
+    __threadfence_system();
+    lbcomm::st_release_sys(p.flags[threadIdx.x] + ((size_t)p.me * p.G + blockIdx.x), p.call);
+    if (!lbcomm::flag_wait_ge(p.flags[p.me] + ((size_t)threadIdx.x * p.G + blockIdx.x), p.call, p.wait_ns)) {
+      *s_fail = 1;
+      coll_fail(where);
+    }
+  }
+  __syncthreads();
+  return *s_fail == 0;
+}
+
+__global__ void __launch_bounds__(COLL_THREADS) embed_tp_fwd_kernel(const EmbParams p) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = COLL_THREADS >> 5;
+  const int per = (p.T + p.G - 1) / p.G;
+  const int lo = min(p.T, per * (int)blockIdx.x), hi = min(p.T, lo + per);
+  const int vpr = p.H >> 3;
+  for (int t = lo + warp; t < hi; t += wpb) {
+    const long long id = p.tok[t];
+    if (id < p.v0 || id >= p.v1) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(p.w + (size_t)(id - p.v0) * p.H);
+    if (p.sp) {
+      const int r = t / p.rpr;
+      uint4* dst = reinterpret_cast<uint4*>(p.stage[r] + (size_t)(t - r * p.rpr) * p.H);
+      for (int v = lane; v < vpr; v += 32) dst[v] = src[v];
+    } else {
+      for (int v = lane; v < vpr; v += 32) {
+        const uint4 x = src[v];
+        for (int j = 0; j < p.n; j++) {
+          const int r = (p.me + 1 + j) % p.n;
+          reinterpret_cast<uint4*>(p.stage[r] + (size_t)t * p.H)[v] = x;
+        }
+      }
+    }
+  }
+  if (!emb_exchange(p, &s_fail, 50u)) return;
+  const int klo = p.sp ? max(lo, p.me * p.rpr) : lo, khi = p.sp ? min(hi, (p.me + 1) * p.rpr) : hi;
+  const int base = p.sp ? p.me * p.rpr : 0;
+  for (int t = klo + warp; t < khi; t += wpb) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.stage[p.me] + (size_t)(t - base) * p.H);
+    uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(t - base) * p.H);
+    for (int v = lane; v < vpr; v += 32) dst[v] = __ldcg(src + v);
+  }
+}
+
+__global__ void __launch_bounds__(COLL_THREADS) embed_tp_bwd_kernel(const EmbParams p) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = COLL_THREADS >> 5;
+  const int per = (p.T + p.G - 1) / p.G;
+  const int lo = min(p.T, per * (int)blockIdx.x), hi = min(p.T, lo + per);
+  const int vpr = p.H >> 3;
+  const int base = p.me * p.rpr;
+  for (int t = max(lo, base) + warp; t < min(hi, base + p.rpr); t += wpb) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.dy + (size_t)(t - base) * p.H);
+    uint4* dst = reinterpret_cast<uint4*>(p.stage[p.me] + (size_t)(t - base) * p.H);
+    for (int v = lane; v < vpr; v += 32) dst[v] = src[v];
+  }
+  if (!emb_exchange(p, &s_fail, 51u)) return;
+  for (int t = lo + warp; t < hi; t += wpb) {
+    const long long id = p.tok[t];
+    if (id < p.v0 || id >= p.v1) continue;
+    const int r = t / p.rpr;
+    const bf16* src = p.stage[r] + (size_t)(t - r * p.rpr) * p.H;
+    bf162* dst = reinterpret_cast<bf162*>(p.out + (size_t)(id - p.v0) * p.H);
+    for (int v = lane; v < vpr; v += 32) {
+      const uint4 x = lbcomm::ld_nc_v4(src + v * 8);
+      const bf162* h2 = reinterpret_cast<const bf162*>(&x);
+#pragma unroll
+      for (int i = 0; i < 4; i++) atomicAdd(dst + v * 4 + i, h2[i]);
+    }
+  }
+}
+
 int fill(CollParams& p, const void* in, void* out, void* const* stage_ptrs, void* const* flag_ptrs, long long half_bytes,
          long long chunk_elems, int elem_bytes, long long staged_elems, int n, int me, int G, unsigned int call) {
   if (n < 1 || n > COLL_MAX_RANKS || me < 0 || me >= n || G < 1 || chunk_elems <= 0) return LB_ERR_SHAPE;
@@ -562,6 +665,41 @@ extern "C" int lb_ulysses_a2a(int mode, const void* src, long long src_ld, long 
   p.mode = mode; p.B = B; p.Sl = Sl; p.H = H; p.hl = hl; p.d = d; p.rep = rep; p.inverse = inverse;
   p.n = n; p.me = me; p.G = G; p.call = call; p.wait_ns = g_lb_flag_wait_ns;
   ulysses_a2a_kernel<<<G, COLL_THREADS, 0, (cudaStream_t)stream>>>(p);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}
+
+// Vocab-parallel embedding over peer memory (see embed_tp_fwd_kernel).  tok [T] int64, w this rank's
+// rows [v1 - v0, H]; stage_ptrs[r] / flag_ptrs[r]: rank r's staging buffer of this call's parity
+// ([T / n, H] under sp, else [T, H]) and flag table [n][G] (zeroed once; `call` = 1, 2, ... per table).
+// sp != 0: out receives this rank's T / n rows (T a multiple of n); sp == 0: all T rows.
+extern "C" int lb_embed_tp_fwd(const void* tok, const void* w, void* out, void* const* stage_ptrs, void* const* flag_ptrs,
+                               int T, int H, int v0, int v1, int n, int me, int G, int sp, unsigned int call, void* stream) {
+  if (n < 1 || n > COLL_MAX_RANKS || me < 0 || me >= n || G < 1 || T <= 0 || H <= 0 || (H % 8) || (sp && T % n)) return LB_ERR_SHAPE;
+  if (((uintptr_t)w | (uintptr_t)out) & 15) return LB_ERR_ARG;
+  EmbParams p;
+  p.tok = (const long long*)tok; p.w = (const bf16*)w; p.out = (bf16*)out; p.dy = nullptr;
+  for (int r = 0; r < n; r++) { p.stage[r] = (bf16*)stage_ptrs[r]; p.flags[r] = (unsigned int*)flag_ptrs[r]; }
+  p.T = T; p.H = H; p.v0 = v0; p.v1 = v1; p.n = n; p.me = me; p.G = G; p.sp = sp; p.rpr = sp ? T / n : T;
+  p.call = call; p.wait_ns = g_lb_flag_wait_ns;
+  embed_tp_fwd_kernel<<<G, COLL_THREADS, 0, (cudaStream_t)stream>>>(p);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}
+
+// Gradient of the table under sequence parallelism: dy this rank's [T / n, H] rows, dw [v1 - v0, H]
+// (accumulated into with bf16 atomics: zero it, or pass a gradient to add to).  stage_ptrs[r]: rank
+// r's [T / n, H] staging buffer of this call's parity.
+extern "C" int lb_embed_tp_bwd(const void* tok, const void* dy, void* dw, void* const* stage_ptrs, void* const* flag_ptrs,
+                               int T, int H, int v0, int v1, int n, int me, int G, unsigned int call, void* stream) {
+  if (n < 1 || n > COLL_MAX_RANKS || me < 0 || me >= n || G < 1 || T <= 0 || H <= 0 || (H % 8) || (T % n)) return LB_ERR_SHAPE;
+  if (((uintptr_t)dy | (uintptr_t)dw) & 15) return LB_ERR_ARG;
+  EmbParams p;
+  p.tok = (const long long*)tok; p.w = nullptr; p.out = (bf16*)dw; p.dy = (const bf16*)dy;
+  for (int r = 0; r < n; r++) { p.stage[r] = (bf16*)stage_ptrs[r]; p.flags[r] = (unsigned int*)flag_ptrs[r]; }
+  p.T = T; p.H = H; p.v0 = v0; p.v1 = v1; p.n = n; p.me = me; p.G = G; p.sp = 1; p.rpr = T / n;
+  p.call = call; p.wait_ns = g_lb_flag_wait_ns;
+  embed_tp_bwd_kernel<<<G, COLL_THREADS, 0, (cudaStream_t)stream>>>(p);
   LB_CHECK_LAUNCH();
   return LB_OK;
 }

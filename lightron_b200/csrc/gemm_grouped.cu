@@ -40,12 +40,22 @@ constexpr int NUM_THREADS = 192;
 constexpr int GROUP_M = 8;
 constexpr int MAX_PROBLEMS = 8;
 
+// epi selects the epilogue of a problem:
+//   0  C = acc (+ C when accumulate)
+//   1  SwiGLU forward: B is a fused [2 * half, K] gate | up weight.  Tile tn holds 128 gate columns
+//      (accumulator columns 0..127) and the 128 up columns of the same index (128..255): both go to
+//      C [M, 2 * half] as usual (the backward needs them) and silu(g) * u goes to C2 [M, half].
+//   2  SwiGLU backward: acc is dh [M, half] of the down projection; the epilogue reads g | u from
+//      C2 [M, 2 * half] and writes dg | du to C [M, 2 * half]; dh itself is never stored.
 struct Problem {
   bf16* C;
   long long ldc;
+  bf16* C2;
+  long long ldc2;
   int M, N, K;
   int a_mn, b_mn, accumulate;
   int tiles_m, tiles_n, num_kb;
+  int epi, half;
 };
 
 struct GroupedParams {
@@ -79,7 +89,7 @@ __device__ __forceinline__ void give_up(volatile int* abort_flag, unsigned where
 template <bool A_MN, bool B_MN>
 __device__ __forceinline__ bool produce_tile(const CUtensorMap* ta, const CUtensorMap* tb, int m0, int n0, int num_kb,
                                              uint32_t smem_base, uint32_t bar_base, int& stage, uint32_t& phase,
-                                             volatile int* abort_flag, int k_base = 0) {
+                                             volatile int* abort_flag, int k_base = 0, int b_split = 0) {
   for (int kb = 0; kb < num_kb; kb++) {
     if (!bw::mbar_wait(bar_base + 8u * (STAGES + stage), phase ^ 1u, abort_flag)) return false;
     const uint32_t fb = bar_base + 8u * stage;
@@ -94,7 +104,12 @@ __device__ __forceinline__ bool produce_tile(const CUtensorMap* ta, const CUtens
       for (int j = 0; j < BM / 64; j++) bw::tma_load_2d(sa + j * 8192, ta, m0 + 64 * j, k0, fb);  // box {64 m, 64 k}
     }
     if (!B_MN) {
-      bw::tma_load_2d(sb, tb, k0, n0, fb);                                                      // box {64 k, 256 n}
+      if (b_split > 0) {                       // two boxes {64 k, 128 n}: rows n0.. and b_split + n0.. of B
+        bw::tma_load_2d(sb, tb, k0, n0, fb);
+        bw::tma_load_2d(sb + (BN / 2) * BK * 2, tb, k0, b_split + n0, fb);
+      } else {
+        bw::tma_load_2d(sb, tb, k0, n0, fb);                                                    // box {64 k, 256 n}
+      }
     } else {
 #pragma unroll
       for (int j = 0; j < BN / 64; j++) bw::tma_load_2d(sb + j * 8192, tb, n0 + 64 * j, k0, fb);  // box {64 n, 64 k}
@@ -179,12 +194,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_grouped_kernel(const __gr
         const CUtensorMap* tb = &gp.tb[pi];
         int tm, tn;
         tile_coords(item & 0xFFFFFF, gp.prob[pi], tm, tn);
-        const int m0 = tm * BM, n0 = tn * BN;
+        const int split = gp.prob[pi].epi == 1 ? gp.prob[pi].half : 0;
+        const int m0 = tm * BM, n0 = split ? tn * (BN / 2) : tn * BN;
         const int num_kb = gp.prob[pi].num_kb;
         switch (gp.prob[pi].a_mn * 2 + gp.prob[pi].b_mn) {
-          case 0: ok = produce_tile<false, false>(ta, tb, m0, n0, num_kb, smem_base, bar_base, stage, phase, abort_flag); break;
+          case 0: ok = produce_tile<false, false>(ta, tb, m0, n0, num_kb, smem_base, bar_base, stage, phase, abort_flag, 0, split); break;
           case 1: ok = produce_tile<false, true>(ta, tb, m0, n0, num_kb, smem_base, bar_base, stage, phase, abort_flag); break;
-          case 2: ok = produce_tile<true, false>(ta, tb, m0, n0, num_kb, smem_base, bar_base, stage, phase, abort_flag); break;
+          case 2: ok = produce_tile<true, false>(ta, tb, m0, n0, num_kb, smem_base, bar_base, stage, phase, abort_flag, 0, split); break;
           default: ok = produce_tile<true, true>(ta, tb, m0, n0, num_kb, smem_base, bar_base, stage, phase, abort_flag); break;
         }
         if (!ok) give_up(abort_flag, 1u);
@@ -241,6 +257,80 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_grouped_kernel(const __gr
       const int n0 = tn * BN;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * BN;
       bf16* crow = pC + (size_t)row * ldc + n0;
+      const int epi = gp.prob[pi].epi;
+      if (epi == 1) {
+        // gate | up tile: store both, and silu(g) * u computed from the ROUNDED values (what a
+        // separate pass over the stored matrix would see, and what the backward recomputes from)
+        const int half = gp.prob[pi].half;
+        const int c0 = tn * (BN / 2);
+        bf16* grow = pC + (size_t)row * ldc + c0;
+        bf16* hrow = gp.prob[pi].C2 + (size_t)row * gp.prob[pi].ldc2 + c0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; c++) {
+          uint32_t rg[32], ru[32];
+          bw::tmem_ld32(taddr + c * 32, rg);
+          bw::tmem_ld32(taddr + BN / 2 + c * 32, ru);
+          bw::tmem_ld_wait();
+          if (row < pM) {
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+              if (c0 + c * 32 + g * 8 < half) {
+                float fg[8], fu[8], h[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) { fg[i] = __uint_as_float(rg[g * 8 + i]); fu[i] = __uint_as_float(ru[g * 8 + i]); }
+                const uint4 pg = pack8(fg), pu = pack8(fu);
+                *reinterpret_cast<uint4*>(grow + c * 32 + g * 8) = pg;
+                *reinterpret_cast<uint4*>(grow + half + c * 32 + g * 8) = pu;
+                unpack8(pg, fg);
+                unpack8(pu, fu);
+#pragma unroll
+                for (int i = 0; i < 8; i++) h[i] = fg[i] / (1.f + __expf(-fg[i])) * fu[i];
+                *reinterpret_cast<uint4*>(hrow + c * 32 + g * 8) = pack8(h);
+              }
+            }
+          }
+        }
+        bw::fence_before();
+        __syncwarp();
+        if (lane == 0) bw::mbar_arrive(tempty_bar(acc));
+        continue;
+      }
+      if (epi == 2) {
+        // dh tile of the down projection -> dg | du, with g | u read from C2
+        const int half = gp.prob[pi].half;
+        const bf16* gurow = gp.prob[pi].C2 + (size_t)row * gp.prob[pi].ldc2 + n0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; c++) {
+          uint32_t r[32];
+          bw::tmem_ld32(taddr + c * 32, r);
+          bw::tmem_ld_wait();
+          if (row < pM) {
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+              if (n0 + c * 32 + g * 8 < half) {
+                float d[8], fg[8], fu[8], dg[8], du[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) d[i] = __uint_as_float(r[g * 8 + i]);
+                unpack8(pack8(d), d);                 // the value a stored bf16 dh would have had
+                unpack8(*reinterpret_cast<const uint4*>(gurow + c * 32 + g * 8), fg);
+                unpack8(*reinterpret_cast<const uint4*>(gurow + half + c * 32 + g * 8), fu);
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                  const float sig = 1.f / (1.f + __expf(-fg[i]));
+                  dg[i] = d[i] * fu[i] * sig * (1.f + fg[i] * (1.f - sig));
+                  du[i] = d[i] * fg[i] * sig;
+                }
+                *reinterpret_cast<uint4*>(crow + c * 32 + g * 8) = pack8(dg);
+                *reinterpret_cast<uint4*>(crow + half + c * 32 + g * 8) = pack8(du);
+              }
+            }
+          }
+        }
+        bw::fence_before();
+        __syncwarp();
+        if (lane == 0) bw::mbar_arrive(tempty_bar(acc));
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; c++) {
         uint32_t r[32];
@@ -613,10 +703,17 @@ extern "C" int lb_gemm_grouped_plan(int n, const int* M, const int* N, const int
 // 16-byte aligned, lda / ldb / ldc / N multiples of 8 (M too when a_mn).  accumulate[i] != 0 adds
 // the product to the old contents of C_i.  The first call with a new set of shapes builds and
 // uploads the schedule (two small device allocations, synchronous copies); later calls only launch.
-extern "C" int lb_gemm_grouped(int n, const void* const* A, const void* const* B, void* const* C, const int* M,
-                               const int* N, const int* K, const long long* lda, const long long* ldb,
-                               const long long* ldc, const int* a_mn, const int* b_mn, const int* accumulate,
-                               void* stream) {
+//
+// lb_gemm_grouped_epi additionally takes, per problem, an epilogue selector (see `Problem`), a second
+// matrix C2 with its leading dimension, and `half`:
+//   epi 1: B is a fused [2 * half, K] gate | up weight (b_mn = 0), N = 2 * half, C [M, 2 * half] receives
+//          g | u and C2 [M, half] receives silu(g) * u;
+//   epi 2: N = half, the product is dh; C2 [M, 2 * half] holds g | u and C [M, 2 * half] receives dg | du.
+extern "C" int lb_gemm_grouped_epi(int n, const void* const* A, const void* const* B, void* const* C, const int* M,
+                                   const int* N, const int* K, const long long* lda, const long long* ldb,
+                                   const long long* ldc, const int* a_mn, const int* b_mn, const int* accumulate,
+                                   const int* epi, void* const* C2, const long long* ldc2, const int* half,
+                                   void* stream) {
   if (n < 1 || n > MAX_PROBLEMS) return LB_ERR_SHAPE;
   static thread_local GroupedParams gp;         // 2.5 KB of tensor maps: kept off the stack, one per calling thread
   std::vector<int> key;
@@ -631,11 +728,20 @@ extern "C" int lb_gemm_grouped(int n, const void* const* A, const void* const* B
     if (!a_mn[i]) rc = bw::make_map_bf16(&gp.ta[i], A[i], (uint64_t)K[i], (uint64_t)M[i], (uint64_t)lda[i], BK, BM);
     else          rc = bw::make_map_bf16(&gp.ta[i], A[i], (uint64_t)M[i], (uint64_t)K[i], (uint64_t)lda[i], 64, BK);
     if (rc) return rc;
-    if (!b_mn[i]) rc = bw::make_map_bf16(&gp.tb[i], B[i], (uint64_t)K[i], (uint64_t)N[i], (uint64_t)ldb[i], BK, BN);
+    const int e = epi ? epi[i] : 0;
+    if (e < 0 || e > 2) return LB_ERR_ARG;
+    if (e) {
+      if (!C2 || !ldc2 || !half || !C2[i] || ((uintptr_t)C2[i] & 15) || (ldc2[i] % 8) || half[i] <= 0 || (half[i] % 8)) return LB_ERR_ARG;
+      if (e == 1 && (b_mn[i] || N[i] != 2 * half[i])) return LB_ERR_SHAPE;
+      if (e == 2 && N[i] != half[i]) return LB_ERR_SHAPE;
+      if (accumulate && accumulate[i]) return LB_ERR_ARG;
+    }
+    if (!b_mn[i]) rc = bw::make_map_bf16(&gp.tb[i], B[i], (uint64_t)K[i], (uint64_t)N[i], (uint64_t)ldb[i], BK, e == 1 ? BN / 2 : BN);
     else          rc = bw::make_map_bf16(&gp.tb[i], B[i], (uint64_t)N[i], (uint64_t)K[i], (uint64_t)ldb[i], 64, BK);
     if (rc) return rc;
     Problem& p = gp.prob[i];
     p.C = (bf16*)C[i]; p.ldc = ldc[i]; p.M = M[i]; p.N = N[i]; p.K = K[i];
+    p.C2 = e ? (bf16*)C2[i] : nullptr; p.ldc2 = e ? ldc2[i] : 0; p.epi = e; p.half = e ? half[i] : 0;
     p.a_mn = a_mn[i]; p.b_mn = b_mn[i]; p.accumulate = accumulate ? accumulate[i] : 0;
     p.tiles_m = (M[i] + BM - 1) / BM; p.tiles_n = (N[i] + BN - 1) / BN; p.num_kb = (K[i] + BK - 1) / BK;
     key.push_back(M[i]); key.push_back(N[i]); key.push_back(K[i]);
@@ -676,6 +782,14 @@ extern "C" int lb_gemm_grouped(int n, const void* const* A, const void* const* B
   return LB_OK;
 }
 
+
+extern "C" int lb_gemm_grouped(int n, const void* const* A, const void* const* B, void* const* C, const int* M,
+                               const int* N, const int* K, const long long* lda, const long long* ldb,
+                               const long long* ldc, const int* a_mn, const int* b_mn, const int* accumulate,
+                               void* stream) {
+  return lb_gemm_grouped_epi(n, A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, accumulate, nullptr, nullptr, nullptr, nullptr,
+                             stream);
+}
 
 // Expert GEMMs over ragged row segments (see gemm_ragged_kernel).  seg: device table of 2 * LE + 2
 // ints (offsets, counts, ...), LE <= 8 local experts.

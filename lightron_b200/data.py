@@ -45,9 +45,14 @@ class SyntheticTokens:
         return self.num_samples
 
     def batch(self, first: int, count: int) -> torch.Tensor:
+        # sample i is a function of (seed, i) alone: the same global batch holds the same rows however
+        # it is cut into micro-batches or spread over data-parallel ranks
         g = torch.Generator()
-        g.manual_seed(self.seed * 1_000_003 + first)
-        return torch.randint(0, self.vocab_size, (count, self.seq_len + 1), generator=g, dtype=torch.int64)
+        rows = []
+        for i in range(first, first + count):
+            g.manual_seed(self.seed * 1_000_003 + i)
+            rows.append(torch.randint(0, self.vocab_size, (self.seq_len + 1,), generator=g, dtype=torch.int64))
+        return torch.stack(rows)
 
 
 class TokenBlocks:

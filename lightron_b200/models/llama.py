@@ -80,6 +80,8 @@ class MLP(nn.Module):
 
     def forward(self, x: torch.Tensor, sp: Optional[bool] = None) -> torch.Tensor:
         sp = self.sp if sp is None else sp
+        if self.tp_group is None:
+            return OF.swiglu_mlp(x, self.w1.weight, self.w3.weight, self.w2.weight)
         if sp:
             gu = fused.all_gather_linear(x, (self.w1.weight, self.w3.weight), self.tp_group)
         else:
@@ -196,6 +198,11 @@ class LightronTransformer(nn.Module):
         """tokens [B, S] -> [T, H] (rows sharded over TP under sequence parallelism)."""
         flat = tokens.reshape(-1)
         if self.args.tp_size > 1:
+            from ..parallel import embed_fused
+            if embed_fused.fused_ok(self.tok_embeddings.weight, self.tp_group, flat.numel(), self.sp):
+                # the owner of a token's id stores its row straight into the rank that needs it
+                return embed_fused.vocab_parallel_embedding(flat, self.tok_embeddings.weight, self.tp_group,
+                                                            self.tok_embeddings.vocab_start, self.sp)
             part = OF.embedding(flat, self.tok_embeddings.weight, self.tok_embeddings.vocab_start)
             if self.sp:
                 return comm.scatter_rows(part, self.tp_group)

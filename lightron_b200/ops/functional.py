@@ -62,29 +62,46 @@ def gemm_grouped(problems) -> List[torch.Tensor]:
     """Several independent GEMMs in one persistent launch (``lb_gemm_grouped``): short tiles of one
     problem fill the idle tail of another.  ``problems``: up to 8 tuples
     ``(a, b, a_mn, b_mn, out_or_None, accumulate)`` with the conventions of :func:`gemm`;
-    ``accumulate`` adds the product to the old contents of ``out``.  Returns the outputs."""
+    ``accumulate`` adds the product to the old contents of ``out``.  A tuple may carry three more
+    entries ``(epi, c2, half)`` that select a SwiGLU epilogue: ``epi = 1`` (``b`` is a fused
+    ``[2 * half, K]`` gate | up weight; ``out [M, 2 * half]`` receives g | u and ``c2 [M, half]``
+    receives ``silu(g) * u``) or ``epi = 2`` (the product is the gradient of ``silu(g) * u``; ``c2``
+    holds g | u and ``out [M, 2 * half]`` receives dg | du).  Returns the outputs."""
     n = len(problems)
     assert 1 <= n <= 8
     import ctypes
     PA, IA, LA = ctypes.c_void_p * n, ctypes.c_int * n, ctypes.c_longlong * n
-    A, B, C = PA(), PA(), PA()
-    M, N, K, amn, bmn, acc = IA(), IA(), IA(), IA(), IA(), IA()
-    lda, ldb, ldc = LA(), LA(), LA()
+    A, B, C, C2 = PA(), PA(), PA(), PA()
+    M, N, K, amn, bmn, acc, epi, half = IA(), IA(), IA(), IA(), IA(), IA(), IA(), IA()
+    lda, ldb, ldc, ldc2 = LA(), LA(), LA(), LA()
     outs = []
-    for i, (a, b, a_mn, b_mn, out, accumulate) in enumerate(problems):
+    any_epi = False
+    for i, prob in enumerate(problems):
+        a, b, a_mn, b_mn, out, accumulate = prob[:6]
+        e, c2, hf = prob[6:9] if len(prob) > 6 else (0, None, 0)
         assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
         m, k = (a.shape[1], a.shape[0]) if a_mn else a.shape
         nn_, kb = (b.shape[1], b.shape[0]) if b_mn else b.shape
         assert k == kb, f"K mismatch {k} vs {kb}"
         if out is None:
             assert not accumulate
-            out = torch.empty(m, nn_, dtype=a.dtype, device=a.device)
+            out = torch.empty(m, 2 * hf if e == 2 else nn_, dtype=a.dtype, device=a.device)
         A[i], B[i], C[i] = a.data_ptr(), b.data_ptr(), out.data_ptr()
         M[i], N[i], K[i] = m, nn_, k
         lda[i], ldb[i], ldc[i] = a.stride(0), b.stride(0), out.stride(0)
         amn[i], bmn[i], acc[i] = int(a_mn), int(b_mn), int(accumulate)
+        epi[i], half[i] = int(e), int(hf)
+        if e:
+            any_epi = True
+            assert c2 is not None and c2.stride(1) == 1 and c2.shape[0] == m and out.shape[1] == 2 * hf
+            assert c2.shape[1] == (hf if e == 1 else 2 * hf)
+            C2[i], ldc2[i] = c2.data_ptr(), c2.stride(0)
         outs.append(out)
-    native.call("lb_gemm_grouped", n, A, B, C, M, N, K, lda, ldb, ldc, amn, bmn, acc, native.stream_ptr())
+    if any_epi:
+        native.call("lb_gemm_grouped_epi", n, A, B, C, M, N, K, lda, ldb, ldc, amn, bmn, acc, epi, C2, ldc2, half,
+                    native.stream_ptr())
+    else:
+        native.call("lb_gemm_grouped", n, A, B, C, M, N, K, lda, ldb, ldc, amn, bmn, acc, native.stream_ptr())
     return outs
 
 
@@ -164,47 +181,110 @@ class _Linear(torch.autograd.Function):
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        sizes = [w.shape[0] for w in ws]
-        dx = None
-        if _GROUP_BWD and ctx.fused and ctx.needs_input_grad[0] and any(ctx.needs_input_grad[1:]):
-            # data gradient and weight gradient in one launch: the short dgrad tiles fill the
-            # last, partly empty wave of the wgrad
-            params = ctx.params
-            if _DIRECT_WGRAD and all(ctx.needs_input_grad[1:]) and direct_wgrad_ok(params):
-                # the weight gradient accumulates straight into the gradient arena in the GEMM
-                # epilogue: no separate add, and the optimizer's bucket hooks are called by hand
-                gout = _as_strided_cat([w.grad for w in params])
-                dx = gemm_grouped([(dy2, x2, True, True, gout, True),
-                                   (dy2, _as_strided_cat(ws), False, True, None, False)])[1]
-                for w in params:
-                    for hook in getattr(w, "_lb_grad_hooks", ()):
-                        hook(w)
-                return (dx.view(ctx.xshape), *([None] * len(ws)))
-            dx, dw = gemm_grouped([(dy2, x2, True, True, None, False),
-                                   (dy2, _as_strided_cat(ws), False, True, None, False)])[::-1]
-            dws, off = [], 0
-            for n in sizes:
-                dws.append(dw[off:off + n])
-                off += n
-            return (dx.view(ctx.xshape), *dws)
-        if ctx.needs_input_grad[0]:
-            if ctx.fused:
-                dx = gemm(dy2, _as_strided_cat(ws), b_mn=True)
-            else:
-                off = 0
-                for w, n in zip(ws, sizes):
-                    part = gemm(dy2[:, off:off + n], w, b_mn=True)
-                    dx = part if dx is None else dx.add_(part)
-                    off += n
-            dx = dx.view(ctx.xshape)
-        dws: List[Optional[torch.Tensor]] = [None] * len(ws)
-        if any(ctx.needs_input_grad[1:]):
-            dw = gemm(dy2, x2, a_mn=True, b_mn=True)        # [sum n_i, K]
+        dx, dws = _linear_backward(x2, ws, ctx.params, dy2, ctx.fused, ctx.needs_input_grad[0], ctx.needs_input_grad[1:])
+        return (None if dx is None else dx.view(ctx.xshape), *dws)
+
+
+def _linear_backward(x2, ws, params, dy2, fused, need_x, need_ws):
+    """Gradients of ``y = x2 [W_0; W_1; ...]^T``: (dx2 or None, one entry per weight; None where the
+    gradient was accumulated straight into the optimizer's arena)."""
+    sizes = [w.shape[0] for w in ws]
+    dx = None
+    if _GROUP_BWD and fused and need_x and any(need_ws):
+        # data gradient and weight gradient in one launch: the short dgrad tiles fill the
+        # last, partly empty wave of the wgrad
+        if _DIRECT_WGRAD and all(need_ws) and direct_wgrad_ok(params):
+            # the weight gradient accumulates straight into the gradient arena in the GEMM
+            # epilogue: no separate add, and the optimizer's bucket hooks are called by hand
+            gout = _as_strided_cat([w.grad for w in params])
+            dx = gemm_grouped([(dy2, x2, True, True, gout, True),
+                               (dy2, _as_strided_cat(ws), False, True, None, False)])[1]
+            for w in params:
+                for hook in getattr(w, "_lb_grad_hooks", ()):
+                    hook(w)
+            return dx, [None] * len(ws)
+        dx, dw = gemm_grouped([(dy2, x2, True, True, None, False),
+                               (dy2, _as_strided_cat(ws), False, True, None, False)])[::-1]
+        dws, off = [], 0
+        for n in sizes:
+            dws.append(dw[off:off + n])
+            off += n
+        return dx, dws
+    if need_x:
+        if fused:
+            dx = gemm(dy2, _as_strided_cat(ws), b_mn=True)
+        else:
             off = 0
-            for i, n in enumerate(sizes):
-                dws[i] = dw[off:off + n]
+            for w, n in zip(ws, sizes):
+                part = gemm(dy2[:, off:off + n], w, b_mn=True)
+                dx = part if dx is None else dx.add_(part)
                 off += n
-        return (dx, *dws)
+    dws: List[Optional[torch.Tensor]] = [None] * len(ws)
+    if any(need_ws):
+        dw = gemm(dy2, x2, a_mn=True, b_mn=True)        # [sum n_i, K]
+        off = 0
+        for i, n in enumerate(sizes):
+            dws[i] = dw[off:off + n]
+            off += n
+    return dx, dws
+
+
+_FUSED_SWIGLU = os.environ.get("LIGHTRON_FUSED_SWIGLU", "1") != "0"
+
+
+class _SwiGLUMLP(torch.autograd.Function):
+    """``(silu(x W1^T) * (x W3^T)) W2^T`` with the activation inside the GEMM epilogues: the gate | up
+    GEMM writes ``silu(g) * u`` next to g | u, and the data-gradient GEMM of the down projection
+    turns its tile of dh into dg | du before storing, so neither the activation nor its gradient is
+    a pass of its own (model/model.py:69 of the reference is ``w2(F.silu(w1(x)) * w3(x))``)."""
+
+    @staticmethod
+    def forward(ctx, x, w1, w3, w2):
+        x2 = x.reshape(-1, x.shape[-1])
+        F_ = w1.shape[0]
+        gu = torch.empty(x2.shape[0], 2 * F_, dtype=x.dtype, device=x.device)
+        h = torch.empty(x2.shape[0], F_, dtype=x.dtype, device=x.device)
+        gemm_grouped([(x2, _as_strided_cat((w1, w3)), False, False, gu, False, 1, h, F_)])
+        y = gemm(h, w2)
+        ctx.save_for_backward(x2, gu, h, w1, w3, w2)
+        ctx.params = (w1, w3, w2)
+        ctx.xshape = x.shape
+        return y.view(*x.shape[:-1], y.shape[-1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, gu, h, w1, w3, w2 = ctx.saved_tensors
+        p1, p3, p2 = ctx.params
+        F_ = w1.shape[0]
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        need = ctx.needs_input_grad
+        dgu = torch.empty_like(gu)
+        act = (dy2, w2, False, True, dgu, False, 2, gu, F_)          # dh = dy W2, stored as dg | du
+        dw2 = None
+        if need[3] and _DIRECT_WGRAD and direct_wgrad_ok((p2,)):
+            gemm_grouped([(dy2, h, True, True, p2.grad, True), act])
+            for hook in getattr(p2, "_lb_grad_hooks", ()):
+                hook(p2)
+        elif need[3]:
+            dw2 = gemm_grouped([(dy2, h, True, True, None, False), act])[0]
+        else:
+            gemm_grouped([act])
+        dx, (dw1, dw3) = _linear_backward(x2, (w1, w3), (p1, p3), dgu, True, need[0], need[1:3])
+        return (None if dx is None else dx.view(ctx.xshape), dw1, dw3, dw2)
+
+
+def swiglu_mlp_ok(x: torch.Tensor, w1, w3, w2) -> bool:
+    return bool(_FUSED_SWIGLU and native.use_native(x) and x.shape[-1] % 8 == 0 and w1.shape[0] % 8 == 0
+                and w2.shape[0] % 8 == 0 and w1.shape == w3.shape and _rows_adjacent((w1, w3)) and w2.is_contiguous())
+
+
+def swiglu_mlp(x: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+    """``w2(silu(w1 x) * w3 x)`` for [n, K] weights; the fused-epilogue kernels when they apply."""
+    if swiglu_mlp_ok(x, w1, w3, w2):
+        return _SwiGLUMLP.apply(x, w1, w3, w2)
+    return linear(swiglu(linear(x, w1, w3)), w2)
 
 
 def _grouped_launch(problems) -> None:

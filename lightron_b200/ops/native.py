@@ -49,6 +49,9 @@ _SIGNATURES = {
     "lb_add_inplace": [_P, _P, _L, _P],
     "lb_gemm_bf16": [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _I, _P],
     "lb_gemm_grouped": [_I] + [_P] * 13,
+    "lb_gemm_grouped_epi": [_I] + [_P] * 17,
+    "lb_embed_tp_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, ctypes.c_uint, _P],
+    "lb_embed_tp_bwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, ctypes.c_uint, _P],
     "lb_gemm_grouped_status": [_P],
     "lb_gemm_grouped_cached": [],
     "lb_gemm_grouped_plan": [_I, _P, _P, _P, _I, _P],
@@ -112,6 +115,9 @@ def _load() -> Optional[ctypes.CDLL]:
         fn.argtypes = args
         fn.restype = c_int
     _LIB = lib
+    wait_ms = os.environ.get("LIGHTRON_FLAG_WAIT_MS")     # limit of every device-side wait for a peer
+    if wait_ms and hasattr(lib, "lb_set_flag_wait_ns"):
+        lib.lb_set_flag_wait_ns(int(float(wait_ms) * 1e6))
     return _LIB
 
 

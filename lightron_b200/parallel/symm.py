@@ -84,6 +84,23 @@ class Workspace:
         self.ag_uses = [0] * self.n_gather   # how often each gather buffer has been a destination
         self.generation = [0] * self.n_gather
         self.rs_target = [0, 0]
+        self.ag_blocks = [None] * self.n_gather   # row blocks of the last gather into each buffer
+        self.rs_bpr = [None, None]                # row blocks per rank of the last reduce-scatter per receive area
+
+    def resync(self) -> None:
+        """Collective: zero every counter.  The counters of a buffer grow by a fixed amount per use, per
+        128-row block; when a call uses a buffer with another number of blocks than the call before
+        (a different token count: rare, e.g. an evaluation batch) the blocks would disagree about the
+        target, so all ranks drain their streams, zero their counters and start counting afresh."""
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)            # nobody is still adding to anybody's counters
+        self.buf[: self.data_off].zero_()
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        self.ag_uses = [0] * self.n_gather
+        self.rs_target = [0, 0]
+        self.ag_blocks = [None] * self.n_gather
+        self.rs_bpr = [None, None]
 
     def gather_off(self, slot: int) -> int:
         return self.data_off + slot * self.gather_bytes
@@ -100,13 +117,16 @@ class Workspace:
             arr[r] = self.ptrs[r] + off
         return arr
 
-    def next_gather_slot(self, keep: bool) -> int:
+    def next_gather_slot(self, keep: bool, blocks: int) -> int:
         if keep:
             slot = self.keep_calls % self.keep_slots
             self.keep_calls += 1
         else:
             slot = self.keep_slots + self.scratch_calls % 2
             self.scratch_calls += 1
+        if self.ag_blocks[slot] not in (None, blocks):
+            self.resync()
+        self.ag_blocks[slot] = blocks
         self.ag_uses[slot] += 1
         self.generation[slot] += 1
         return slot
@@ -179,7 +199,7 @@ def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, k
     M = rows * n
     N = w.shape[1] if b_mn else w.shape[0]
     ws = workspace(group, M * K * 2, 0, x_local.device)
-    slot = ws.next_gather_slot(keep)
+    slot = ws.next_gather_slot(keep, M // _BM)
     target = ws.ag_uses[slot] * _MOVER_WARPS
     y = torch.empty(M, N, dtype=x_local.dtype, device=x_local.device)
     # CTAs that push rows instead of doing MMAs: a short GEMM needs the gather done quickly (more
@@ -209,6 +229,9 @@ def gemm_rs(x: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False) -> torc
     ws.rs_calls += 1
     bpr = M // n // _BM
     assert bpr <= _MAX_BPR
+    if ws.rs_bpr[slot] not in (None, bpr):
+        ws.resync()
+    ws.rs_bpr[slot] = bpr
     ws.rs_target[slot] += 4 * ((N + 255) // 256)
     out = torch.empty(M // n, N, dtype=x.dtype, device=x.device)
     recv = ws.ptr_array(ws.recv_off(slot))

@@ -113,6 +113,12 @@ class VocabParallelEmbedding(nn.Module):
         self.weight.tp_shard_dim = 0
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+        if self.tp > 1:
+            from . import embed_fused
+            sp = self.sequence_parallel and tokens.dim() == 1
+            if (tokens.dim() == 1 or not self.sequence_parallel) and embed_fused.fused_ok(self.weight, self.group, tokens.numel(), sp):
+                out = embed_fused.vocab_parallel_embedding(tokens, self.weight, self.group, self.vocab_start, sp)
+                return out if sp else out.view(*tokens.shape, self.embedding_dim)
         part = OF.embedding(tokens, self.weight, self.vocab_start)
         if self.tp == 1:
             return part

@@ -137,7 +137,7 @@ class _UlyssesAttention(torch.autograd.Function):
         pool = _pool(group, B, Sl, hq, hkv, d, qkv.device)
         W = (hq + 2 * hkv) * d
         qkv2 = qkv.view(B * Sl, W)
-        keep = torch.is_grad_enabled() and qkv.requires_grad
+        keep = bool(ctx.needs_input_grad[0])      # (grad mode itself is off inside forward)
         slot = pool.acquire(keep)
         ld = qkv2.stride(0)
         # sequence shards -> head shards, q and k rotated on the way
@@ -150,8 +150,10 @@ class _UlyssesAttention(torch.autograd.Function):
         pool.a2a(1, o, 0, 0, slot["o"], hq * d, 0, 0, pool.hql, 1)
         ctx.save_for_backward(o, lse, cos, sin, positions)
         ctx.slot, ctx.pool, ctx.dims = slot, pool, (B, Sl, hq, hkv, d, scale)
-        out = slot["o"]["t"]
-        return out
+        ctx.keep = keep
+        # a fresh view object per call: the buffer's own tensor object would carry the autograd
+        # history of the layer (or step) that used the slot before
+        return slot["o"]["t"].view(B * Sl, hq * d)
 
     @staticmethod
     def backward(ctx, dout):
@@ -180,7 +182,8 @@ class _UlyssesAttention(torch.autograd.Function):
             dqkv[:, hq * d:(hq + hkv) * d].copy_(gs["dk"]["t"])
             dqkv[:, (hq + hkv) * d:].copy_(gs["dv"]["t"])
         OF._rope_native_(dqkv, cos, sin, positions, Sl, hq + hkv, d, True)     # un-rotate the q and k gradients
-        pool.release(slot)
+        if ctx.keep:
+            pool.release(slot)
         return dqkv.view(B * Sl, W), None, None, None, None, None, None, None, None, None, None
 
 

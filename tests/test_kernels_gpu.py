@@ -207,6 +207,37 @@ def test_swiglu_fwd_bwd():
     assert _rel_err(gu.grad, gf.grad) < 1e-2
 
 
+@pytest.mark.parametrize("T,K,I", [(300, 256, 688), (1024, 512, 1408), (2048, 2048, 5632)])
+def test_swiglu_mlp_fused_epilogues(T, K, I):
+    """Gate | up GEMM with the activation in its epilogue, and the down projection's data gradient with
+    the activation's backward in its epilogue: same bits as the three-launch path, and close to fp32."""
+    from lightron_b200.ops import functional as OF
+    ws = _rand(2 * I + K, max(K, I), scale=0.03, seed=3)
+    w13 = ws[:2 * I, :K].contiguous()
+    w1, w3 = w13[:I].requires_grad_(True), w13[I:].requires_grad_(True)
+    w2 = ws[2 * I:, :I].contiguous().requires_grad_(True)
+    x = _rand(T, K, seed=4).requires_grad_(True)
+    dy = _rand(T, K, seed=5)
+    assert OF.swiglu_mlp_ok(x, w1, w3, w2)
+    y = OF.swiglu_mlp(x, w1, w3, w2)
+    y.backward(dy)
+    got = [y.detach().clone()] + [t.grad.clone() for t in (x, w1, w3, w2)]
+    for t in (x, w1, w3, w2):
+        t.grad = None
+    y2 = OF.linear(OF.swiglu(OF.linear(x, w1, w3)), w2)
+    y2.backward(dy)
+    want = [y2.detach()] + [t.grad for t in (x, w1, w3, w2)]
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    xf, w1f, w3f, w2f = [t.detach().float().requires_grad_(True) for t in (x, w1, w3, w2)]
+    yf = (torch.nn.functional.silu(xf @ w1f.t()) * (xf @ w3f.t())) @ w2f.t()
+    yf.backward(dy.float())
+    assert _rel_err(got[0], yf) < 1e-2
+    for a, b in zip(got[1:], (xf.grad, w1f.grad, w3f.grad, w2f.grad)):
+        assert _rel_err(a, b) < 2e-2
+    assert _gemm_status()[0] == 0
+
+
 def test_embedding_fwd_bwd_vocab_parallel():
     from lightron_b200.ops import functional as OF
     V, H, T = 1000, 256, 4096
