@@ -64,6 +64,15 @@ def main() -> None:
     peer = hdl.get_buffer((rank + 1) % world, (nbytes,), torch.uint8)
     t_copy, _ = bench(lambda: peer.copy_(src, non_blocking=True))
     link_gbs = nbytes / t_copy / 1e6
+    # the same transfer issued by SMs (lb_peer_copy): 16-byte stores by every thread, and bulk copies
+    # through shared memory issued by one thread per CTA, for several CTA counts
+    from lightron_b200.ops import native
+    sm_rates = []
+    for mode, label in ((0, "16-byte stores"), (1, "bulk copies via shared memory")):
+        for ctas in (8, 16, 32, 64, 148):
+            t_sm, _ = bench(lambda: native.call("lb_peer_copy", src.data_ptr(), peer.data_ptr(), nbytes, mode, ctas,
+                                                native.stream_ptr()), iters=5)
+            sm_rates.append((label, ctas, nbytes / t_sm / 1e6))
     rows = []
     for name, N, K in [("qkv", 2560 // world, 2048), ("gate+up", 11264 // world, 2048), ("LM head", 32000 // world, 2048),
                        ("dgrad of down (dy gathered)", 5632 // world, 2048), ("dgrad of wo (dy gathered)", 2048 // world, 2048)]:
@@ -92,6 +101,8 @@ def main() -> None:
     symm.check_status()
     if rank == 0:
         print(f"peer copy (copy engine, 256 MiB): {link_gbs:.0f} GB/s per direction; {world} ranks, {T} tokens")
+        print("peer copy issued by SMs (256 MiB), GB/s per direction: " +
+              "; ".join(f"{label} x {c} CTAs: {r:.0f}" for label, c, r in sm_rates))
         print("| fused path | ours, rows moved by SM stores (ms) | ours, rows moved by copy engines (ms) | library collective + GEMM (ms) "
               "| GEMM alone (ms) | bytes / link rate (ms) | roofline (ms) | best fraction of roofline | SM MHz |")
         print("|---|---|---|---|---|---|---|---|---|")

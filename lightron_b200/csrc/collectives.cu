@@ -14,6 +14,7 @@
 // CTA b of its peers, so no CTA waits for another CTA of its own GPU and the kernels do not depend
 // on all G CTAs being resident together.  All waits are bounded (comm.cuh) and report through
 // lb_coll_status().
+#include "tcgen05.cuh"
 #include "comm.cuh"
 
 static __device__ unsigned int g_coll_status[4] = {0, 0, 0, 0};
@@ -528,6 +529,80 @@ __global__ void __launch_bounds__(COLL_THREADS) embed_tp_bwd_kernel(const EmbPar
   }
 }
 
+// ---- plain copy into a peer's memory, two ways (the movers of the fused kernels are built on these) ---
+// mode 0: every thread loads 16 bytes from local memory and stores them to the destination (UNR loads
+//         in flight per thread);
+// mode 1: the copy engine of the SM does the work: one thread per CTA issues bulk copies
+//         global -> shared (cp.async.bulk, completion on an mbarrier) and shared -> global
+//         (cp.async.bulk, bulk groups) of CHUNK bytes through a ring of STAGES buffers; no data passes
+//         through registers and every NVLink write is a full CHUNK.
+constexpr int PC_CHUNK = 16384, PC_STAGES = 4;
+
+__global__ void __launch_bounds__(COLL_THREADS) peer_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                                                 long long nvec, int mode) {
+  if (mode == 0) {
+    constexpr int UNR = 8;
+    const long long stride = (long long)gridDim.x * COLL_THREADS;
+    long long i = (long long)blockIdx.x * COLL_THREADS + threadIdx.x;
+    for (; i + (UNR - 1) * stride < nvec; i += UNR * stride) {
+      uint4 v[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; u++) v[u] = src[i + u * stride];
+#pragma unroll
+      for (int u = 0; u < UNR; u++) dst[i + u * stride] = v[u];
+    }
+    for (; i < nvec; i += stride) dst[i] = src[i];
+    return;
+  }
+  extern __shared__ uint8_t pc_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pc_smem_raw) + 127) & ~(uintptr_t)127);
+  __shared__ uint64_t bars[PC_STAGES];
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PC_STAGES; s++) bw::mbar_init(bw::smem_u32(&bars[s]), 1);
+    bw::mbar_init_fence();
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  const long long bytes = nvec * 16;
+  const long long nchunks = (bytes + PC_CHUNK - 1) / PC_CHUNK;
+  const uint8_t* s8 = reinterpret_cast<const uint8_t*>(src);
+  uint8_t* d8 = reinterpret_cast<uint8_t*>(dst);
+  // chunk c of this CTA is global chunk blockIdx.x + c * gridDim.x; loads run STAGES - 1 chunks ahead
+  const long long mine = (nchunks - blockIdx.x + gridDim.x - 1) / gridDim.x;
+  auto chunk_bytes = [&](long long c) {
+    const long long off = (blockIdx.x + c * gridDim.x) * (long long)PC_CHUNK;
+    return (unsigned)min((long long)PC_CHUNK, bytes - off);
+  };
+  auto issue_load = [&](long long c) {
+    const int st = (int)(c % PC_STAGES);
+    const long long off = (blockIdx.x + c * gridDim.x) * (long long)PC_CHUNK;
+    const unsigned nb = chunk_bytes(c);
+    const uint32_t bar = bw::smem_u32(&bars[st]);
+    bw::mbar_expect_tx(bar, nb);
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(bw::smem_u32(smem + st * PC_CHUNK)), "l"(s8 + off), "r"(nb), "r"(bar) : "memory");
+  };
+  for (long long c = 0; c < min(mine, (long long)PC_STAGES - 1); c++) issue_load(c);
+  for (long long c = 0; c < mine; c++) {
+    const int st = (int)(c % PC_STAGES);
+    const uint32_t phase = (uint32_t)((c / PC_STAGES) & 1);
+    int spins = 0;
+    while (!bw::mbar_test_wait(bw::smem_u32(&bars[st]), phase)) {
+      if (++spins > (1 << 24)) { coll_fail(60u); return; }
+    }
+    const long long off = (blockIdx.x + c * gridDim.x) * (long long)PC_CHUNK;
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 ::"l"(d8 + off), "r"(bw::smem_u32(smem + st * PC_CHUNK)), "r"(chunk_bytes(c)) : "memory");
+    bw::bulk_commit();
+    if (c + PC_STAGES - 1 < mine) {
+      // the buffer the next load overwrites was the source of the store issued one iteration ago
+      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      issue_load(c + PC_STAGES - 1);
+    }
+  }
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
 int fill(CollParams& p, const void* in, void* out, void* const* stage_ptrs, void* const* flag_ptrs, long long half_bytes,
          long long chunk_elems, int elem_bytes, long long staged_elems, int n, int me, int G, unsigned int call) {
   if (n < 1 || n > COLL_MAX_RANKS || me < 0 || me >= n || G < 1 || chunk_elems <= 0) return LB_ERR_SHAPE;
@@ -700,6 +775,26 @@ extern "C" int lb_embed_tp_bwd(const void* tok, const void* dy, void* dw, void* 
   p.T = T; p.H = H; p.v0 = v0; p.v1 = v1; p.n = n; p.me = me; p.G = G; p.sp = 1; p.rpr = T / n;
   p.call = call; p.wait_ns = g_lb_flag_wait_ns;
   embed_tp_bwd_kernel<<<G, COLL_THREADS, 0, (cudaStream_t)stream>>>(p);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}
+
+// Copy `bytes` (a multiple of 16) from local memory to dst, which may be a peer's memory, with `ctas`
+// CTAs.  mode 0: 16-byte loads and stores by every thread; mode 1: bulk copies through shared memory
+// issued by one thread per CTA.  The measured rate of this call is the ceiling of what the movers inside
+// the fused kernels can reach.
+extern "C" int lb_peer_copy(const void* src, void* dst, long long bytes, int mode, int ctas, void* stream) {
+  if (bytes <= 0 || (bytes % 16) || ctas < 1 || mode < 0 || mode > 1) return LB_ERR_SHAPE;
+  if (((uintptr_t)src | (uintptr_t)dst) & 15) return LB_ERR_ARG;
+  const int smem = mode == 1 ? PC_STAGES * PC_CHUNK + 128 : 0;
+  if (mode == 1) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaFuncSetAttribute(peer_copy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PC_STAGES * PC_CHUNK + 128);
+      attr_set = true;
+    }
+  }
+  peer_copy_kernel<<<ctas, COLL_THREADS, smem, (cudaStream_t)stream>>>((const uint4*)src, (uint4*)dst, bytes / 16, mode);
   LB_CHECK_LAUNCH();
   return LB_OK;
 }

@@ -371,26 +371,11 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       if (m_i != -INFINITY && (m_new - m_i) * sl2 <= 8.f) m_new = m_i;
       const float m_s = (m_new == -INFINITY) ? 0.f : m_new * sl2;
       const float corr = (m_i == -INFINITY) ? 0.f : exp2f(m_i * sl2 - m_s);
-      if (j > 0) {
-        // previous P V finished: O is stable and the P columns may be overwritten
-        if (!mbar_wait(pv_done(t), (uint32_t)(j - 1) & 1u, abort_flag)) { ok = false; break; }
-        fence_after();
-        if (__any_sync(0xffffffffu, m_new != m_i)) {
-#pragma unroll 1
-          for (int c = 0; c < D / 32; c++) {
-            uint32_t o[32];
-            tmem_ld32(to_addr + c * 32, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-            tmem_st32(to_addr + c * 32, o);
-          }
-          tmem_st_wait();
-        }
-      }
       FA_T(3);
       // exponentials; P goes back to TMEM as packed bf16 pairs (column c holds keys 2c, 2c+1), 32
-      // columns per store so that the first store is in flight while the second half is computed
+      // columns per store so that the first store is in flight while the second half is computed.
+      // The first half is computed BEFORE waiting for the previous P V (which still reads the P
+      // columns and owns O): its 64 exponentials overlap the tail of that MMA.
       float rs2[2] = {0.f, 0.f};
 #pragma unroll
       for (int hh = 0; hh < 2; hh++) {
@@ -404,6 +389,23 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
           bf162 pk = __floats2bfloat162_rn(e0, e1);
           pr[c] = *reinterpret_cast<uint32_t*>(&pk);
         }
+        if (hh == 0 && j > 0) {
+          // previous P V finished: O is stable and the P columns may be overwritten
+          if (!mbar_wait(pv_done(t), (uint32_t)(j - 1) & 1u, abort_flag)) { ok = false; }
+          fence_after();
+          if (ok && __any_sync(0xffffffffu, m_new != m_i)) {
+#pragma unroll 1
+            for (int c = 0; c < D / 32; c++) {
+              uint32_t o[32];
+              tmem_ld32(to_addr + c * 32, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+              tmem_st32(to_addr + c * 32, o);
+            }
+            tmem_st_wait();
+          }
+        }
         if (C::P_TMEM) {
           tmem_st32(tp_addr + hh * 32, pr);
         } else {
@@ -414,6 +416,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
                 make_uint4(pr[c16 * 4], pr[c16 * 4 + 1], pr[c16 * 4 + 2], pr[c16 * 4 + 3]);
         }
       }
+      if (!ok) break;
       if (C::P_TMEM) tmem_st_wait(); else fence_proxy_async_smem();
       l_i = l_i * corr + (rs2[0] + rs2[1]);
       m_i = m_new;

@@ -191,45 +191,41 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   if (MODE == 1 && (int)blockIdx.x < cp.n_comm) {
     // ---------------- all-gather mover CTAs (no tensor-core work, no TMEM) ----------------
-    // unit = (destination rank, 128-row block of this rank's rows).  Every warp copies its share of
-    // the block's rows (two rows = 2 x K x 2 bytes in flight per warp), fences, and adds one to the
-    // destination's counter of that block; warps never wait for each other, so while one sits in
-    // its fence the others keep streaming.  Peers first, the local copy last.
+    // unit = (destination rank, 128-row block of this rank's rows).  The CTA copies the block, fences,
+    // and adds MOVER_WARPS to the destination's counter of that block.  Peers first, the local copy last.
     const int units = cp.n_ranks * cp.blocks_per_rank;
     const int vec_per_row = p.K / 8;
+    const int unit_vecs = BM * vec_per_row;
+    const size_t src_row = (size_t)cp.ld_x / 8;
+    constexpr int UNR = 8;
     for (int u = blockIdx.x; u < units; u += cp.n_comm) {
       const int dst_rank = (cp.rank + 1 + u / cp.blocks_per_rank) % cp.n_ranks;
       const int rb = u % cp.blocks_per_rank;
       const uint4* sp = reinterpret_cast<const uint4*>(cp.x_local + (size_t)rb * BM * cp.ld_x);
       uint4* dp = reinterpret_cast<uint4*>(cp.gather[dst_rank] + ((size_t)cp.rank * cp.rows_per_rank + (size_t)rb * BM) * p.K);
-      const size_t src_row = (size_t)cp.ld_x / 8;
-      // each warp owns rows warp, warp+6, ...; it keeps 4 rows x 4 vectors (256 B per lane) in flight
-      for (int r = warp; r < BM; r += 4 * MOVER_WARPS) {
-        for (int v0 = 0; v0 < vec_per_row; v0 += 32 * 4) {
-          uint4 a[4][4];
+      // the block is one flat run of 16-byte vectors in the destination; consecutive threads take
+      // consecutive vectors and every thread keeps UNR loads in flight before it stores them (the
+      // pattern that reaches ~85 % of the copy-engine rate with 16 CTAs, see lb_peer_copy)
+      int i = threadIdx.x;
+      for (; i + (UNR - 1) * NUM_THREADS < unit_vecs; i += UNR * NUM_THREADS) {
+        uint4 a[UNR];
 #pragma unroll
-          for (int q = 0; q < 4; q++) {
-            const int rr = r + q * MOVER_WARPS;
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-              const int v = v0 + j * 32 + lane;
-              if (rr < BM && v < vec_per_row) a[q][j] = sp[(size_t)rr * src_row + v];
-            }
-          }
-#pragma unroll
-          for (int q = 0; q < 4; q++) {
-            const int rr = r + q * MOVER_WARPS;
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-              const int v = v0 + j * 32 + lane;
-              if (rr < BM && v < vec_per_row) dp[(size_t)rr * vec_per_row + v] = a[q][j];
-            }
-          }
+        for (int q = 0; q < UNR; q++) {
+          const int e = i + q * NUM_THREADS;
+          const int rr = e / vec_per_row;
+          a[q] = sp[(size_t)rr * src_row + (e - rr * vec_per_row)];
         }
+#pragma unroll
+        for (int q = 0; q < UNR; q++) dp[i + q * NUM_THREADS] = a[q];
       }
+      for (; i < unit_vecs; i += NUM_THREADS) {
+        const int rr = i / vec_per_row;
+        dp[i] = sp[(size_t)rr * src_row + (i - rr * vec_per_row)];
+      }
+      // one count of MOVER_WARPS per block (the consumer's target is uses x MOVER_WARPS)
       __threadfence_system();
-      __syncwarp();
-      if (lane == 0) red_release_sys_add(cp.ag_flags[dst_rank] + cp.rank * cp.blocks_per_rank + rb, 1u);
+      __syncthreads();
+      if (threadIdx.x == 0) red_release_sys_add(cp.ag_flags[dst_rank] + cp.rank * cp.blocks_per_rank + rb, (unsigned)MOVER_WARPS);
     }
     return;
   }
@@ -333,9 +329,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int quad = warp & 3;  // TMEM lane quadrant this warp may access
     bool ok = true;
     int it = 0;
-    constexpr int RS_MAX_PEND = 24;
-    unsigned int* rs_pend[RS_MAX_PEND];     // MODE 2: counters of tiles whose stores are not yet fenced
-    int rs_npend = 0, rs_pend_owner = -1;
+    constexpr int RS_MAX_PEND = 2;
+    unsigned int* rs_pend[RS_MAX_PEND];     // MODE 2: counter of the tile whose stores are not yet fenced
+    int rs_npend = 0;
     for (int t = cta; t < p.num_tiles && ok; t += n_cta, it++) {
       const int acc = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
@@ -343,6 +339,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       map_tile(t, tm, tn);
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4u)) { ok = false; break; }
       tcgen05_fence_after();
+      if (MODE == 2 && rs_npend > 0) {
+        // Count the tile stored before this one.  Its stores had the whole wait above to drain, so
+        // the system-scope fence is short, and the owner learns of the tile one tile time after it
+        // was produced: by the time the owner turns to its own rows (its last tiles), the partials of
+        // those rows, which the peers produce FIRST, have long been counted.
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0)
+          for (int i = 0; i < rs_npend; i++) red_release_sys_add(rs_pend[i], 1u);
+        rs_npend = 0;
+      }
       const int row = tm * BM + quad * 32 + lane;
       const int n0 = tn * BN;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * BN;
@@ -425,17 +432,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(acc));       // accumulator free: the next tile may start
-        // Counting a tile needs a system-scope fence after its stores, which costs microseconds.
-        // Tiles are ordered by destination rank, so the counts of one destination are batched:
-        // one fence when the destination changes (or the batch is full), then all its increments.
-        if (rs_npend > 0 && (owner != rs_pend_owner || rs_npend == RS_MAX_PEND)) {
-          __threadfence_system();
-          __syncwarp();
-          if (lane == 0)
-            for (int i = 0; i < rs_npend; i++) red_release_sys_add(rs_pend[i], 1u);
-          rs_npend = 0;
-        }
-        rs_pend_owner = owner;
+        // the tile is counted (fence + one increment) when the next tile's accumulator is ready
         rs_pend[rs_npend++] = cp.rs_flags[owner] + cp.rank * cp.blocks_per_rank + lb;
         const int nvec = min(BN, p.N - n0) / 8;            // 16-byte vectors per row (<= 32)
         bf16* dst0 = cp.recv[owner] + ((size_t)cp.rank * cp.rows_per_rank + (size_t)lb * BM + quad * 32) * p.N + n0;

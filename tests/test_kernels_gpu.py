@@ -238,6 +238,20 @@ def test_swiglu_mlp_fused_epilogues(T, K, I):
     assert _gemm_status()[0] == 0
 
 
+@pytest.mark.parametrize("mode", [0, 1], ids=["stores", "bulk"])
+@pytest.mark.parametrize("nbytes,ctas", [(16, 1), (16384 * 3 + 4096 + 16, 2), ((8 << 20) + 48, 16), (64 << 20, 148)])
+def test_peer_copy_kernel_local(mode, nbytes, ctas):
+    """The SM-issued copy the fused kernels' movers are built on (here into local memory)."""
+    from lightron_b200.ops import native
+    src = torch.randint(0, 255, (nbytes,), device="cuda", dtype=torch.uint8)
+    dst = torch.zeros(nbytes + 64, device="cuda", dtype=torch.uint8)
+    native.call("lb_peer_copy", src.data_ptr(), dst.data_ptr(), nbytes, mode, ctas, native.stream_ptr())
+    torch.cuda.synchronize()
+    assert torch.equal(dst[:nbytes], src)
+    assert int(dst[nbytes:].sum()) == 0
+    assert not native.device_status()
+
+
 def test_embedding_fwd_bwd_vocab_parallel():
     from lightron_b200.ops import functional as OF
     V, H, T = 1000, 256, 4096
