@@ -102,7 +102,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   if ((int)blockIdx.x < push.n_mov) {
     // ------------------------------- K/V mover CTAs -------------------------------
     // unit = (destination rank, batch, which of this rank's two chunks, 128-row block, K or V)
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int nwarps = blockDim.x >> 5;
     const int bpc = push.chunk_rows / 128;
     const int fpb = (2 * push.n_ranks * push.chunk_rows) / 128;       // flag words per batch
     const int units = push.n_ranks * p.B * 2 * bpc * 2;
@@ -120,21 +120,33 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       const bf16* src = kv ? push.v_src : push.k_src;
       const long long ts = kv ? push.v_ts : push.k_ts;
       bf16* dstp = (kv ? push.v_dst[dst] : push.k_dst[dst]) + grow0 * push.row_elems;
-      for (int r = warp; r < 128; r += nwarps) {
-        const uint4* sp = reinterpret_cast<const uint4*>(src + (lrow0 + r) * ts);
-        uint4* dp = reinterpret_cast<uint4*>(dstp + (long long)r * push.row_elems);
-        for (int v0 = 0; v0 < vec_per_row; v0 += 128) {
-          uint4 a[4];
+      // the block is one flat run of 16-byte vectors in the destination: consecutive threads take
+      // consecutive vectors, UNR loads in flight per thread before the stores
+      constexpr int UNR = 4;
+      const int unit_vecs = 128 * vec_per_row;
+      const uint4* sp = reinterpret_cast<const uint4*>(src + lrow0 * ts);
+      uint4* dp = reinterpret_cast<uint4*>(dstp);
+      const long long src_row = ts / 8;
+      int i = threadIdx.x;
+      for (; i + (UNR - 1) * FA_FWD_THREADS < unit_vecs; i += UNR * FA_FWD_THREADS) {
+        uint4 a[UNR];
 #pragma unroll
-          for (int j = 0; j < 4; j++) if (v0 + j * 32 + lane < vec_per_row) a[j] = sp[v0 + j * 32 + lane];
-#pragma unroll
-          for (int j = 0; j < 4; j++) if (v0 + j * 32 + lane < vec_per_row) dp[v0 + j * 32 + lane] = a[j];
+        for (int q = 0; q < UNR; q++) {
+          const int e = i + q * FA_FWD_THREADS;
+          const int rr = e / vec_per_row;
+          a[q] = sp[rr * src_row + (e - rr * vec_per_row)];
         }
+#pragma unroll
+        for (int q = 0; q < UNR; q++) dp[i + q * FA_FWD_THREADS] = a[q];
+      }
+      for (; i < unit_vecs; i += FA_FWD_THREADS) {
+        const int rr = i / vec_per_row;
+        dp[i] = sp[rr * src_row + (i - rr * vec_per_row)];
       }
       __threadfence_system();
-      __syncwarp();
-      if (lane == 0)
-        lbcomm::red_release_sys_add(push.flags[dst] + (grow0 >> 7), 1u);
+      __syncthreads();
+      if (threadIdx.x == 0)
+        lbcomm::red_release_sys_add(push.flags[dst] + (grow0 >> 7), (unsigned)nwarps);   // one count per warp, as the target expects
     }
     return;
   }

@@ -251,10 +251,22 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_grouped_kernel(const __gr
       const long long ldc = gp.prob[pi].ldc;
       const int acc = n & 1;
       const uint32_t acc_phase = (uint32_t)(n >> 1) & 1u;
-      if (!bw::mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { give_up(abort_flag, 4u); break; }
-      bw::fence_after();
       const int row = tm * BM + quad * 32 + lane;
       const int n0 = tn * BN;
+      if (gp.prob[pi].epi == 2 && row < pM) {
+        // while the MMAs of this tile run: pull the g | u values its epilogue will read into L2
+        const bf16* pre = gp.prob[pi].C2 + (size_t)row * gp.prob[pi].ldc2 + n0;
+        const int half = gp.prob[pi].half;
+#pragma unroll
+        for (int l = 0; l < BN / 64; l++) {
+          if (n0 + l * 64 < half) {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(pre + l * 64));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(pre + half + l * 64));
+          }
+        }
+      }
+      if (!bw::mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { give_up(abort_flag, 4u); break; }
+      bw::fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * BN;
       bf16* crow = pC + (size_t)row * ldc + n0;
       const int epi = gp.prob[pi].epi;
@@ -296,15 +308,29 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_grouped_kernel(const __gr
         continue;
       }
       if (epi == 2) {
-        // dh tile of the down projection -> dg | du, with g | u read from C2
+        // dh tile of the down projection -> dg | du, with g | u read from C2.  The 8 loads of a
+        // 32-column chunk are issued together, and the chunk after it is already in flight, before
+        // anything is stored (a store in between would order the loads behind it).
         const int half = gp.prob[pi].half;
         const bf16* gurow = gp.prob[pi].C2 + (size_t)row * gp.prob[pi].ldc2 + n0;
-#pragma unroll 1
+        const bool row_ok = row < pM;
+        uint4 gq[2][4], uq[2][4];
+        auto fetch = [&](int c, int buf) {
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            const bool ok = row_ok && (n0 + c * 32 + g * 8 < half);
+            gq[buf][g] = ok ? __ldg(reinterpret_cast<const uint4*>(gurow + c * 32 + g * 8)) : make_uint4(0, 0, 0, 0);
+            uq[buf][g] = ok ? __ldg(reinterpret_cast<const uint4*>(gurow + half + c * 32 + g * 8)) : make_uint4(0, 0, 0, 0);
+          }
+        };
+        fetch(0, 0);
+#pragma unroll
         for (int c = 0; c < BN / 32; c++) {
+          if (c + 1 < BN / 32) fetch(c + 1, (c + 1) & 1);
           uint32_t r[32];
           bw::tmem_ld32(taddr + c * 32, r);
           bw::tmem_ld_wait();
-          if (row < pM) {
+          if (row_ok) {
 #pragma unroll
             for (int g = 0; g < 4; g++) {
               if (n0 + c * 32 + g * 8 < half) {
@@ -312,8 +338,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_grouped_kernel(const __gr
 #pragma unroll
                 for (int i = 0; i < 8; i++) d[i] = __uint_as_float(r[g * 8 + i]);
                 unpack8(pack8(d), d);                 // the value a stored bf16 dh would have had
-                unpack8(*reinterpret_cast<const uint4*>(gurow + c * 32 + g * 8), fg);
-                unpack8(*reinterpret_cast<const uint4*>(gurow + half + c * 32 + g * 8), fu);
+                unpack8(gq[c & 1][g], fg);
+                unpack8(uq[c & 1][g], fu);
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
                   const float sig = 1.f / (1.f + __expf(-fg[i]));

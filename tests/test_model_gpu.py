@@ -46,6 +46,7 @@ def test_moe_grouped_expert_gemm_matches_per_expert_loop(monkeypatch):
     from lightron_b200.ops import functional as OF, native
     from lightron_b200.optim import DistributedAdamW
     mesh.set_context(None)
+    monkeypatch.setenv("LIGHTRON_FUSED_EP", "0")        # this test is about the library-exchange path (the kernel chain has its own)
     dev = torch.device("cuda", 0)
     args = ModelArgs(dim=256, n_layers=2, n_heads=8, n_kv_heads=4, vocab_size=1024, intermediate_size=512,
                      max_seq_len=128, moe_num_experts=4, moe_topk=2, moe_layer_freq=1)
