@@ -538,6 +538,64 @@ __global__ void __launch_bounds__(COLL_THREADS) embed_tp_bwd_kernel(const EmbPar
 //         through registers and every NVLink write is a full CHUNK.
 constexpr int PC_CHUNK = 16384, PC_STAGES = 4;
 
+// modes 2 and 3 copy in chunks and publish every chunk the way the movers of the fused kernels do
+// (a system-scope fence, then one release-add on a flag word in the destination's memory), so that the
+// cost of that protocol can be measured without a GEMM around it:
+// mode 2: all threads copy a chunk, fence, CTA barrier, thread 0 adds to the chunk's flag;
+// mode 3: warps 0-6 copy and hand finished chunks to warp 7 through shared-memory barriers; warp 7
+//         fences and adds to the flag while the others are already copying the next chunk.
+__global__ void __launch_bounds__(COLL_THREADS) peer_copy_flag_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                                                      long long nvec, int mode, long long chunk_vecs,
+                                                                      unsigned int* flags) {
+  constexpr int UNR = 8;
+  const long long nchunks = (nvec + chunk_vecs - 1) / chunk_vecs;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __shared__ uint64_t full[4];
+  __shared__ int done;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 4; i++) bw::mbar_init(bw::smem_u32(&full[i]), 7);
+    done = 0;
+    bw::mbar_init_fence();
+  }
+  __syncthreads();
+  const int nthr = mode == 2 ? COLL_THREADS : COLL_THREADS - 32;
+  int j = 0;
+  for (long long c = blockIdx.x; c < nchunks; c += gridDim.x, j++) {
+    const long long lo = c * chunk_vecs, hi = min(nvec, lo + chunk_vecs);
+    if (mode == 2 || warp < 7) {
+      if (mode == 3 && j >= 4) {
+        int spins = 0;
+        while (*reinterpret_cast<volatile int*>(&done) < j - 3)
+          if (++spins > (1 << 26)) { coll_fail(61u); return; }
+      }
+      long long i = lo + threadIdx.x;
+      for (; i + (UNR - 1) * nthr < hi; i += UNR * nthr) {
+        uint4 v[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; u++) v[u] = src[i + u * nthr];
+#pragma unroll
+        for (int u = 0; u < UNR; u++) dst[i + u * nthr] = v[u];
+      }
+      for (; i < hi; i += nthr) dst[i] = src[i];
+      if (mode == 2) {
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) lbcomm::red_release_sys_add(flags + c, 1u);
+      } else {
+        __syncwarp();
+        if (lane == 0) bw::mbar_arrive(bw::smem_u32(&full[j & 3]));
+      }
+    } else if (lane == 0) {
+      bool got = false;
+      for (uint32_t spin = 0; spin < (1u << 26) && !got; spin++) got = bw::mbar_try_wait(bw::smem_u32(&full[j & 3]), (uint32_t)(j >> 2) & 1u);
+      if (!got) { coll_fail(62u); return; }
+      __threadfence_system();
+      lbcomm::red_release_sys_add(flags + c, 1u);
+      *reinterpret_cast<volatile int*>(&done) = j + 1;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(COLL_THREADS) peer_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
                                                                  long long nvec, int mode) {
   if (mode == 0) {
@@ -783,6 +841,18 @@ extern "C" int lb_embed_tp_bwd(const void* tok, const void* dy, void* dw, void* 
 // CTAs.  mode 0: 16-byte loads and stores by every thread; mode 1: bulk copies through shared memory
 // issued by one thread per CTA.  The measured rate of this call is the ceiling of what the movers inside
 // the fused kernels can reach.
+// modes 2 / 3 (see peer_copy_flag_kernel): `chunk_bytes` per published chunk, `flags`: one zeroed u32
+// per chunk in the destination GPU's memory.
+extern "C" int lb_peer_copy_flagged(const void* src, void* dst, long long bytes, int mode, int ctas, long long chunk_bytes,
+                                    void* flags, void* stream) {
+  if (bytes <= 0 || (bytes % 16) || ctas < 1 || mode < 2 || mode > 3 || chunk_bytes < 16 || (chunk_bytes % 16) || !flags) return LB_ERR_SHAPE;
+  if (((uintptr_t)src | (uintptr_t)dst) & 15) return LB_ERR_ARG;
+  peer_copy_flag_kernel<<<ctas, COLL_THREADS, 0, (cudaStream_t)stream>>>((const uint4*)src, (uint4*)dst, bytes / 16, mode,
+                                                                        chunk_bytes / 16, (unsigned int*)flags);
+  LB_CHECK_LAUNCH();
+  return LB_OK;
+}
+
 extern "C" int lb_peer_copy(const void* src, void* dst, long long bytes, int mode, int ctas, void* stream) {
   if (bytes <= 0 || (bytes % 16) || ctas < 1 || mode < 0 || mode > 1) return LB_ERR_SHAPE;
   if (((uintptr_t)src | (uintptr_t)dst) & 15) return LB_ERR_ARG;

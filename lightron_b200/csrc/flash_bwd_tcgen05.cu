@@ -157,7 +157,7 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NBAR);
-  __shared__ int s_abort;
+  __shared__ int s_abort[2];     // {abort, extra wait in ms}: see bw::mbar_wait
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t sbase = smem_u32(smem);
@@ -185,7 +185,8 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   const int total_it = per_head * rep;
 
   if (threadIdx.x == 0) {
-    s_abort = 0;
+    s_abort[0] = 0;
+    s_abort[1] = 0;
     mbar_init(kv_full, 1);
     for (int s = 0; s < C::QS; s++) { mbar_init(q_full(s), 1); mbar_init(q_empty(s), 1); }
     for (int s = 0; s < C::DS; s++) { mbar_init(do_full(s), 1); mbar_init(do_empty(s), 1); }
@@ -204,7 +205,7 @@ fa_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   __syncthreads();
   fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  volatile int* abort_flag = &s_abort;
+  volatile int* abort_flag = s_abort;
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------

@@ -69,6 +69,23 @@ struct FaFwdParams {
   unsigned long long wait_ns;    // limit of a wait on a key block's arrival flag
 };
 
+// 2^x on the FMA pipe: round to the nearest integer with the 1.5 * 2^23 trick, a degree-4 polynomial
+// for the fraction in [-0.5, 0.5] (relative error 6e-5, far below the bf16 rounding of P), and
+// the integer part added to the exponent field.  Inputs below -126 (masked scores are -inf) give ~0.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float t = x + 12582912.f;
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(f, 9.6181291e-3f, 5.5504109e-2f);
+  p = fmaf(p, f, 2.4022651e-1f);
+  p = fmaf(p, f, 6.9314718e-1f);
+  p = fmaf(p, f, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+#ifndef LB_FA_POLY_EVERY
+#define LB_FA_POLY_EVERY 4
+#endif
+
 template <int D>
 struct FaCfg {
   static constexpr int BM = 128, BN = 128;
@@ -102,7 +119,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   if ((int)blockIdx.x < push.n_mov) {
     // ------------------------------- K/V mover CTAs -------------------------------
     // unit = (destination rank, batch, which of this rank's two chunks, 128-row block, K or V)
-    const int nwarps = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int bpc = push.chunk_rows / 128;
     const int fpb = (2 * push.n_ranks * push.chunk_rows) / 128;       // flag words per batch
     const int units = push.n_ranks * p.B * 2 * bpc * 2;
@@ -120,33 +137,23 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       const bf16* src = kv ? push.v_src : push.k_src;
       const long long ts = kv ? push.v_ts : push.k_ts;
       bf16* dstp = (kv ? push.v_dst[dst] : push.k_dst[dst]) + grow0 * push.row_elems;
-      // the block is one flat run of 16-byte vectors in the destination: consecutive threads take
-      // consecutive vectors, UNR loads in flight per thread before the stores
-      constexpr int UNR = 4;
-      const int unit_vecs = 128 * vec_per_row;
-      const uint4* sp = reinterpret_cast<const uint4*>(src + lrow0 * ts);
-      uint4* dp = reinterpret_cast<uint4*>(dstp);
-      const long long src_row = ts / 8;
-      int i = threadIdx.x;
-      for (; i + (UNR - 1) * FA_FWD_THREADS < unit_vecs; i += UNR * FA_FWD_THREADS) {
-        uint4 a[UNR];
+      // every warp copies its share of the block's rows, fences and counts by itself: while one warp
+      // sits in its fence the others keep streaming
+      for (int r = warp; r < 128; r += nwarps) {
+        const uint4* sp = reinterpret_cast<const uint4*>(src + (lrow0 + r) * ts);
+        uint4* dp = reinterpret_cast<uint4*>(dstp + (long long)r * push.row_elems);
+        for (int v0 = 0; v0 < vec_per_row; v0 += 128) {
+          uint4 a[4];
 #pragma unroll
-        for (int q = 0; q < UNR; q++) {
-          const int e = i + q * FA_FWD_THREADS;
-          const int rr = e / vec_per_row;
-          a[q] = sp[rr * src_row + (e - rr * vec_per_row)];
+          for (int j = 0; j < 4; j++) if (v0 + j * 32 + lane < vec_per_row) a[j] = sp[v0 + j * 32 + lane];
+#pragma unroll
+          for (int j = 0; j < 4; j++) if (v0 + j * 32 + lane < vec_per_row) dp[v0 + j * 32 + lane] = a[j];
         }
-#pragma unroll
-        for (int q = 0; q < UNR; q++) dp[i + q * FA_FWD_THREADS] = a[q];
-      }
-      for (; i < unit_vecs; i += FA_FWD_THREADS) {
-        const int rr = i / vec_per_row;
-        dp[i] = sp[rr * src_row + (i - rr * vec_per_row)];
       }
       __threadfence_system();
-      __syncthreads();
-      if (threadIdx.x == 0)
-        lbcomm::red_release_sys_add(push.flags[dst] + (grow0 >> 7), (unsigned)nwarps);   // one count per warp, as the target expects
+      __syncwarp();
+      if (lane == 0)
+        lbcomm::red_release_sys_add(push.flags[dst] + (grow0 >> 7), 1u);
     }
     return;
   }
@@ -154,7 +161,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NBAR);
-  __shared__ int s_abort;
+  __shared__ int s_abort[2];     // {abort, extra wait in ms}: see bw::mbar_wait
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t sbase = smem_u32(smem);
@@ -191,7 +198,8 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   const int nb_max = max(nb[0], nb[1]);
 
   if (threadIdx.x == 0) {
-    s_abort = 0;
+    s_abort[0] = 0;
+    s_abort[1] = p.kv_flags ? wait_extra_ms(p.wait_ns) : 0;
     mbar_init(q_full, 1);
     for (int s = 0; s < C::KS; s++) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 2); }
     for (int s = 0; s < C::VS; s++) { mbar_init(v_full(s), 1); mbar_init(v_empty(s), 2); }
@@ -204,9 +212,19 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   __syncthreads();
   fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  volatile int* abort_flag = &s_abort;
+  volatile int* abort_flag = s_abort;
 
+  // (with LB_FA_SETMAXNREG) warps 0-3 (loads, MMA issue) hand registers to the eight softmax warps,
+  // which hold a 128-column row of scores each
+#ifdef LB_FA_SETMAXNREG
+#define FA_REG_DEC() asm volatile("setmaxnreg.dec.sync.aligned.u32 96;")
+#define FA_REG_INC() asm volatile("setmaxnreg.inc.sync.aligned.u32 200;")
+#else
+#define FA_REG_DEC()
+#define FA_REG_INC()
+#endif
   if (warp == 0) {
+    FA_REG_DEC();
     // ------------------------------- TMA producer -------------------------------
     if (lane == 0 && nb_max > 0) {
       mbar_expect_tx(q_full, 2 * C::TILE_BYTES);
@@ -241,6 +259,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       if (!ok) atomicExch(&g_fa_status[0], 1u);
     }
   } else if (warp == 1 || warp == 2) {
+    FA_REG_DEC();
     // ------------------------------- MMA issuers -------------------------------
     // One issuing thread per query tile.  A tcgen05.mma costs its issuer 60-90 cycles whatever its
     // size (measured: 370 cycles for the four 128x128x16 of one S, 500 for the eight 128x64x16 of
@@ -321,8 +340,11 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       }
       if (!ok) atomicExch(&g_fa_status[0], 2u);
     }
-  } else if (warp >= 4) {
+  } else if (warp == 3) {
+    FA_REG_DEC();
+  } else {
     // ------------------------------- softmax warps -------------------------------
+    FA_REG_INC();
     const int t = (warp - 4) >> 2;
     const int quad = warp & 3;
     const int rit = quad * 32 + lane;              // row inside the tile
@@ -333,6 +355,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     const uint32_t tp_addr = lane_addr + C::COL_P + t * C::P_STRIDE;
     uint8_t* sP = smem + C::OFF_P + t * C::P_BYTES;
     const float sl2 = p.scale * 1.4426950408889634f;
+    constexpr int POLY_EVERY = (D == 64) ? LB_FA_POLY_EVERY : 0;   // head_dim 128 has twice the MMA work per exponential
     float m_i = -INFINITY, l_i = 0.f;
     bool ok = true;
     const int n_my = nb[t];
@@ -395,8 +418,16 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 #pragma unroll
         for (int c = 0; c < 32; c++) {
           const int i = hh * 64 + c * 2;
-          const float e0 = exp2f(fmaf(__uint_as_float(r[i]), sl2, -m_s));
-          const float e1 = exp2f(fmaf(__uint_as_float(r[i + 1]), sl2, -m_s));
+          // the MUFU unit (16 exponentials per clock per SM) is this kernel's ceiling at small head
+          // dimensions: every POLY_EVERY-th pair is evaluated on the FMA pipe instead
+          float e0, e1;
+          if (POLY_EVERY > 0 && (c % (POLY_EVERY > 0 ? POLY_EVERY : 1)) == 0) {
+            e0 = exp2_poly(fmaf(__uint_as_float(r[i]), sl2, -m_s));
+            e1 = exp2_poly(fmaf(__uint_as_float(r[i + 1]), sl2, -m_s));
+          } else {
+            e0 = exp2f(fmaf(__uint_as_float(r[i]), sl2, -m_s));
+            e1 = exp2f(fmaf(__uint_as_float(r[i + 1]), sl2, -m_s));
+          }
           rs2[c & 1] += e0 + e1;
           bf162 pk = __floats2bfloat162_rn(e0, e1);
           pr[c] = *reinterpret_cast<uint32_t*>(&pk);

@@ -148,7 +148,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_grouped_kernel(const __gr
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
-  __shared__ int s_abort;
+  __shared__ int s_abort[2];     // {abort, extra wait in ms}: see bw::mbar_wait
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -161,7 +161,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_grouped_kernel(const __gr
   const int item_begin = gp.offsets[blockIdx.x], item_end = gp.offsets[blockIdx.x + 1];
 
   if (threadIdx.x == 0) {
-    s_abort = 0;
+    s_abort[0] = 0;
+    s_abort[1] = 0;
     for (int s = 0; s < STAGES; s++) {
       bw::mbar_init(full_bar(s), 1);
       bw::mbar_init(empty_bar(s), 1);
@@ -177,7 +178,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_grouped_kernel(const __gr
   __syncthreads();
   bw::fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  volatile int* abort_flag = &s_abort;
+  volatile int* abort_flag = s_abort;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -458,7 +459,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_ragged_kernel(const __gri
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
-  __shared__ int s_abort;
+  __shared__ int s_abort[2];     // {abort, extra wait in ms}: see bw::mbar_wait
   __shared__ int s_off[MAX_PROBLEMS], s_tiles[MAX_PROBLEMS];
 
   const int warp = threadIdx.x >> 5;
@@ -471,7 +472,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_ragged_kernel(const __gri
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
 
   if (threadIdx.x == 0) {
-    s_abort = 0;
+    s_abort[0] = 0;
+    s_abort[1] = rp.wait_flag ? bw::wait_extra_ms(rp.wait_ns) : 0;
     for (int s = 0; s < STAGES; s++) {
       bw::mbar_init(full_bar(s), 1);
       bw::mbar_init(empty_bar(s), 1);
@@ -497,7 +499,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_ragged_kernel(const __gri
   __syncthreads();
   bw::fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  volatile int* abort_flag = &s_abort;
+  volatile int* abort_flag = s_abort;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------

@@ -184,36 +184,51 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   // bars: [0,STAGES) full, [STAGES,2*STAGES) empty, then tmem_full[2], tmem_empty[2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
-  __shared__ int s_abort;
+  __shared__ int s_abort[2];     // {abort, extra wait in ms}: see bw::mbar_wait
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (MODE == 1 && (int)blockIdx.x < cp.n_comm) {
     // ---------------- all-gather mover CTAs (no tensor-core work, no TMEM) ----------------
-    // unit = (destination rank, 128-row block of this rank's rows).  The CTA copies the block, fences,
-    // and adds MOVER_WARPS to the destination's counter of that block.  Peers first, the local copy last.
-    const int units = cp.n_ranks * cp.blocks_per_rank;
+    // A block (128 rows of this rank) is one flat run of 16-byte vectors in the destination:
+    // consecutive threads take consecutive vectors, UNR loads in flight per thread before the stores.
+    // Publishing costs a system-scope fence, and on NVLink a fence does not return before everything
+    // the SM has stored to the peer has drained (tens of microseconds behind a deep write queue;
+    // measured with lb_peer_copy_flagged: a fence per 512 KB halves the copy rate).  So a mover CTA
+    // fences ONCE: it stores all its blocks for every peer, fences, and then raises the counters of
+    // those blocks.  To let the first remote tiles start early all the same, the movers work in two
+    // groups: even CTAs push the first half of the blocks at once and copy the local rows afterwards,
+    // odd CTAs copy their local rows first and push the second half of the blocks after that, so the
+    // first half has the link to itself while the GEMM CTAs are still busy with the local rows.
+    const int bpr = cp.blocks_per_rank;
     const int vec_per_row = p.K / 8;
     const int unit_vecs = BM * vec_per_row;
     const size_t src_row = (size_t)cp.ld_x / 8;
+    const bool contig = cp.ld_x == p.K;
     constexpr int UNR = 8;
-    for (int u = blockIdx.x; u < units; u += cp.n_comm) {
-      const int dst_rank = (cp.rank + 1 + u / cp.blocks_per_rank) % cp.n_ranks;
-      const int rb = u % cp.blocks_per_rank;
+    const bool split = cp.n_comm >= 2 && bpr >= 2;
+    const int group = split ? ((int)blockIdx.x & 1) : 0;
+    const int gidx = split ? ((int)blockIdx.x >> 1) : (int)blockIdx.x;
+    const int gctas = split ? ((cp.n_comm + 1 - group) >> 1) : cp.n_comm;
+    const int half0 = (bpr + 1) / 2;
+    const int b_lo = split ? (group == 0 ? 0 : half0) : 0;
+    const int b_hi = split ? (group == 0 ? half0 : bpr) : bpr;
+    auto copy_block = [&](int dst_rank, int rb) {
       const uint4* sp = reinterpret_cast<const uint4*>(cp.x_local + (size_t)rb * BM * cp.ld_x);
       uint4* dp = reinterpret_cast<uint4*>(cp.gather[dst_rank] + ((size_t)cp.rank * cp.rows_per_rank + (size_t)rb * BM) * p.K);
-      // the block is one flat run of 16-byte vectors in the destination; consecutive threads take
-      // consecutive vectors and every thread keeps UNR loads in flight before it stores them (the
-      // pattern that reaches ~85 % of the copy-engine rate with 16 CTAs, see lb_peer_copy)
       int i = threadIdx.x;
       for (; i + (UNR - 1) * NUM_THREADS < unit_vecs; i += UNR * NUM_THREADS) {
         uint4 a[UNR];
 #pragma unroll
         for (int q = 0; q < UNR; q++) {
           const int e = i + q * NUM_THREADS;
-          const int rr = e / vec_per_row;
-          a[q] = sp[(size_t)rr * src_row + (e - rr * vec_per_row)];
+          if (contig) {
+            a[q] = sp[e];
+          } else {
+            const int rr = e / vec_per_row;
+            a[q] = sp[(size_t)rr * src_row + (e - rr * vec_per_row)];
+          }
         }
 #pragma unroll
         for (int q = 0; q < UNR; q++) dp[i + q * NUM_THREADS] = a[q];
@@ -222,10 +237,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int rr = i / vec_per_row;
         dp[i] = sp[(size_t)rr * src_row + (i - rr * vec_per_row)];
       }
-      // one count of MOVER_WARPS per block (the consumer's target is uses x MOVER_WARPS)
+    };
+    auto peer_pass = [&]() {
+      for (int j = 1; j < cp.n_ranks; j++)
+        for (int rb = b_lo + gidx; rb < b_hi; rb += gctas) copy_block((cp.rank + j) % cp.n_ranks, rb);
       __threadfence_system();
       __syncthreads();
-      if (threadIdx.x == 0) red_release_sys_add(cp.ag_flags[dst_rank] + cp.rank * cp.blocks_per_rank + rb, (unsigned)MOVER_WARPS);
+      const int mine = (b_hi - b_lo - gidx + gctas - 1) / gctas;            // blocks of this CTA per peer
+      for (int k = threadIdx.x; k < mine * (cp.n_ranks - 1); k += NUM_THREADS) {
+        const int dst_rank = (cp.rank + 1 + k / mine) % cp.n_ranks;
+        const int rb = b_lo + gidx + (k % mine) * gctas;
+        red_release_sys_add(cp.ag_flags[dst_rank] + cp.rank * bpr + rb, (unsigned)MOVER_WARPS);
+      }
+    };
+    auto local_pass = [&]() {
+      for (int rb = b_lo + gidx; rb < b_hi; rb += gctas) copy_block(cp.rank, rb);
+    };
+    if (gidx < gctas) {
+      if (group == 0) { peer_pass(); local_pass(); }
+      else { local_pass(); peer_pass(); }
     }
     return;
   }
@@ -249,7 +279,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   };
 
   if (threadIdx.x == 0) {
-    s_abort = 0;
+    s_abort[0] = 0;
+    s_abort[1] = (MODE == 0) ? 0 : wait_extra_ms(cp.wait_ns);
     for (int s = 0; s < STAGES; s++) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -269,7 +300,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  volatile int* abort_flag = &s_abort;
+  volatile int* abort_flag = s_abort;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -329,8 +360,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int quad = warp & 3;  // TMEM lane quadrant this warp may access
     bool ok = true;
     int it = 0;
-    constexpr int RS_MAX_PEND = 2;
-    unsigned int* rs_pend[RS_MAX_PEND];     // MODE 2: counter of the tile whose stores are not yet fenced
+    constexpr int RS_MAX_PEND = 24;
+    unsigned int* rs_pend[RS_MAX_PEND];     // MODE 2: counters of tiles whose stores are not yet fenced
     int rs_npend = 0;
     for (int t = cta; t < p.num_tiles && ok; t += n_cta, it++) {
       const int acc = it & 1;
@@ -339,17 +370,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       map_tile(t, tm, tn);
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4u)) { ok = false; break; }
       tcgen05_fence_after();
-      if (MODE == 2 && rs_npend > 0) {
-        // Count the tile stored before this one.  Its stores had the whole wait above to drain, so
-        // the system-scope fence is short, and the owner learns of the tile one tile time after it
-        // was produced: by the time the owner turns to its own rows (its last tiles), the partials of
-        // those rows, which the peers produce FIRST, have long been counted.
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0)
-          for (int i = 0; i < rs_npend; i++) red_release_sys_add(rs_pend[i], 1u);
-        rs_npend = 0;
-      }
       const int row = tm * BM + quad * 32 + lane;
       const int n0 = tn * BN;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * BN;
@@ -383,27 +403,63 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             arrived = false;
         const size_t lrow = (size_t)lb * BM + quad * 32 + lane;           // row inside this rank's [rows_per_rank, N]
         bf16* orow = cp.out + lrow * cp.ld_out + n0;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; c++) {
-          uint32_t r[32];
-          tmem_ld32(taddr + c * 32, r);
-          tmem_ld_wait();
+        // The partials of a 32-column chunk are loaded together (a store between two loads would
+        // order the second load behind it).
+        auto peer_row = [&](int s) { return cp.recv[cp.rank] + ((size_t)s * cp.rows_per_rank + lrow) * p.N + n0; };
+        auto fetch = [&](uint4* q, int s, int c) {
+          const bf16* src = peer_row(s) + c * 32;
 #pragma unroll
-          for (int g = 0; g < 4; g++) {
-            const int col = n0 + c * 32 + g * 8;
-            if (col < p.N && arrived) {
-              float f[8];
+          for (int g = 0; g < 4; g++)
+            q[g] = (arrived && n0 + c * 32 + g * 8 < p.N) ? __ldcg(reinterpret_cast<const uint4*>(src + g * 8)) : make_uint4(0, 0, 0, 0);
+        };
+        auto add_store = [&](float* f, int c) {
 #pragma unroll
-              for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[g * 8 + i]);
-              for (int s = 0; s < cp.n_ranks; s++) {
-                if (s == cp.rank) continue;
-                float o[8];
-                unpack8(__ldcg(reinterpret_cast<const uint4*>(cp.recv[cp.rank] + ((size_t)s * cp.rows_per_rank + lrow) * p.N + col)), o);
+          for (int g = 0; g < 4; g++)
+            if (arrived && n0 + c * 32 + g * 8 < p.N) *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = pack8(f + g * 8);
+        };
+        if (cp.n_ranks == 2) {
+          // one peer: its chunk c + 1 is in flight while chunk c is summed and stored
+          const int s = cp.rank ^ 1;
+          uint4 pq[2][4];
+          fetch(pq[0], s, 0);
 #pragma unroll
-                for (int i = 0; i < 8; i++) f[i] += o[i];
-              }
-              *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = pack8(f);
+          for (int c = 0; c < BN / 32; c++) {
+            if (c + 1 < BN / 32) fetch(pq[(c + 1) & 1], s, c + 1);
+            uint32_t r[32];
+            tmem_ld32(taddr + c * 32, r);
+            tmem_ld_wait();
+            float f[32];
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+              float o[8];
+              unpack8(pq[c & 1][g], o);
+#pragma unroll
+              for (int i = 0; i < 8; i++) f[g * 8 + i] = __uint_as_float(r[g * 8 + i]) + o[i];
             }
+            add_store(f, c);
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; c++) {
+            uint32_t r[32];
+            tmem_ld32(taddr + c * 32, r);
+            tmem_ld_wait();
+            float f[32];
+#pragma unroll
+            for (int i = 0; i < 32; i++) f[i] = __uint_as_float(r[i]);
+            for (int s = 0; s < cp.n_ranks; s++) {
+              if (s == cp.rank) continue;
+              uint4 pq[4];
+              fetch(pq, s, c);
+#pragma unroll
+              for (int g = 0; g < 4; g++) {
+                float o[8];
+                unpack8(pq[g], o);
+#pragma unroll
+                for (int i = 0; i < 8; i++) f[g * 8 + i] += o[i];
+              }
+            }
+            add_store(f, c);
           }
         }
         tcgen05_fence_before();
@@ -432,7 +488,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(acc));       // accumulator free: the next tile may start
-        // the tile is counted (fence + one increment) when the next tile's accumulator is ready
+        // Counting a tile needs a system-scope fence after its stores, and on NVLink that fence does
+        // not return before everything this SM has stored to the peer has drained (tens of
+        // microseconds).  The tiles that travel come first in the tile order, so their counts are
+        // kept and sent together: one fence when this CTA turns to the rows it keeps (or ends, or
+        // the list is full).
+        if (rs_npend == RS_MAX_PEND) {
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0)
+            for (int i = 0; i < rs_npend; i++) red_release_sys_add(rs_pend[i], 1u);
+          rs_npend = 0;
+        }
         rs_pend[rs_npend++] = cp.rs_flags[owner] + cp.rank * cp.blocks_per_rank + lb;
         const int nvec = min(BN, p.N - n0) / 8;            // 16-byte vectors per row (<= 32)
         bf16* dst0 = cp.recv[owner] + ((size_t)cp.rank * cp.rows_per_rank + (size_t)lb * BM + quad * 32) * p.N + n0;

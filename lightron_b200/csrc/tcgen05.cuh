@@ -48,13 +48,34 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  `abort_flag` lives in shared memory: once any role gives up, all others stop too.
+// Bounded wait.  `abort_flag` points at the CTA's control words {abort, extra_ms}: after WAIT_LIMIT
+// polls (about a second) the wait goes on for another extra_ms of wall time before it gives up.
+// Kernels that contain waits for OTHER GPUs set extra_ms to the limit of those waits plus a margin,
+// so that the roles of the pipeline that merely wait for the role that waits for the peer do not give
+// up before it does; kernels without such waits set 0.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 255u) == 255u && *abort_flag) return false;
   }
+  const unsigned long long extra_ns = (unsigned long long)(unsigned)abort_flag[1] * 1000000ull;
+  if (extra_ns) {
+    unsigned long long t0, t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if (*abort_flag) return false;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      if (t - t0 > extra_ns) break;
+    }
+  }
   *abort_flag = 1;
   return false;
+}
+// extra_ms word for a kernel whose peer waits are limited to wait_ns
+__device__ __forceinline__ int wait_extra_ms(unsigned long long wait_ns) {
+  const unsigned long long ms = wait_ns / 1000000ull + 2000ull;
+  return (int)(ms > 0x7fffffffull ? 0x7fffffffull : ms);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {

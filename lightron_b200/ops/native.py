@@ -51,6 +51,7 @@ _SIGNATURES = {
     "lb_gemm_grouped": [_I] + [_P] * 13,
     "lb_gemm_grouped_epi": [_I] + [_P] * 17,
     "lb_peer_copy": [_P, _P, _L, _I, _I, _P],
+    "lb_peer_copy_flagged": [_P, _P, _L, _I, _I, _L, _P, _P],
     "lb_embed_tp_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, ctypes.c_uint, _P],
     "lb_embed_tp_bwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, ctypes.c_uint, _P],
     "lb_gemm_grouped_status": [_P],

@@ -209,7 +209,7 @@ def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, k
         n_comm = -1                 # copy-engine transfers on a side stream, all SMs on the GEMM
     elif n_comm <= 0:
         flops = 2.0 * M * N * K
-        n_comm = 16 if flops < 6e11 else 8        # 16 mover CTAs already reach ~630 GB/s (bench_comm's copy table)
+        n_comm = 32 if flops < 1.2e11 else (16 if flops < 6e11 else 8)
     gathers = ws.ptr_array(ws.gather_off(slot))
     flags = ws.ptr_array(ws.ag_flag_off + slot * _MAX_BLOCKS * 4)
     native.call("lb_gemm_ag", w.data_ptr(), y.data_ptr(), M, N, K, w.stride(0), y.stride(0), int(b_mn), n, ws.rank,
