@@ -191,71 +191,50 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   if (MODE == 1 && (int)blockIdx.x < cp.n_comm) {
     // ---------------- all-gather mover CTAs (no tensor-core work, no TMEM) ----------------
-    // A block (128 rows of this rank) is one flat run of 16-byte vectors in the destination:
-    // consecutive threads take consecutive vectors, UNR loads in flight per thread before the stores.
-    // Publishing costs a system-scope fence, and on NVLink a fence does not return before everything
-    // the SM has stored to the peer has drained (tens of microseconds behind a deep write queue;
-    // measured with lb_peer_copy_flagged: a fence per 512 KB halves the copy rate).  So a mover CTA
-    // fences ONCE: it stores all its blocks for every peer, fences, and then raises the counters of
-    // those blocks.  To let the first remote tiles start early all the same, the movers work in two
-    // groups: even CTAs push the first half of the blocks at once and copy the local rows afterwards,
-    // odd CTAs copy their local rows first and push the second half of the blocks after that, so the
-    // first half has the link to itself while the GEMM CTAs are still busy with the local rows.
-    const int bpr = cp.blocks_per_rank;
+    // unit = (destination rank, 128-row block of this rank's rows).  Every warp copies its share of
+    // the block's rows (two rows = 2 x K x 2 bytes in flight per warp), fences, and adds one to the
+    // destination's counter of that block; warps never wait for each other, so while one sits in
+    // its fence the others keep streaming.  Peers first, the local copy last.
+    // (Measured alternatives on 2 GPUs, all slower inside this kernel although a plain copy kernel with
+    // the same access pattern moves 630 GB/s with 16 CTAs: flat CTA-wide copies with one fence per block,
+    // a signalling warp that fences while the others copy, and one fence per CTA after all its blocks.
+    // A system-scope fence here does not return before the SM's queued peer stores have drained, so
+    // what counts is that the warps of a CTA reach their fences at different times.)
+    const int units = cp.n_ranks * cp.blocks_per_rank;
     const int vec_per_row = p.K / 8;
-    const int unit_vecs = BM * vec_per_row;
-    const size_t src_row = (size_t)cp.ld_x / 8;
-    const bool contig = cp.ld_x == p.K;
-    constexpr int UNR = 8;
-    const bool split = cp.n_comm >= 2 && bpr >= 2;
-    const int group = split ? ((int)blockIdx.x & 1) : 0;
-    const int gidx = split ? ((int)blockIdx.x >> 1) : (int)blockIdx.x;
-    const int gctas = split ? ((cp.n_comm + 1 - group) >> 1) : cp.n_comm;
-    const int half0 = (bpr + 1) / 2;
-    const int b_lo = split ? (group == 0 ? 0 : half0) : 0;
-    const int b_hi = split ? (group == 0 ? half0 : bpr) : bpr;
-    auto copy_block = [&](int dst_rank, int rb) {
+    for (int u = blockIdx.x; u < units; u += cp.n_comm) {
+      const int dst_rank = (cp.rank + 1 + u / cp.blocks_per_rank) % cp.n_ranks;
+      const int rb = u % cp.blocks_per_rank;
       const uint4* sp = reinterpret_cast<const uint4*>(cp.x_local + (size_t)rb * BM * cp.ld_x);
       uint4* dp = reinterpret_cast<uint4*>(cp.gather[dst_rank] + ((size_t)cp.rank * cp.rows_per_rank + (size_t)rb * BM) * p.K);
-      int i = threadIdx.x;
-      for (; i + (UNR - 1) * NUM_THREADS < unit_vecs; i += UNR * NUM_THREADS) {
-        uint4 a[UNR];
+      const size_t src_row = (size_t)cp.ld_x / 8;
+      // each warp owns rows warp, warp+6, ...; it keeps 4 rows x 4 vectors (256 B per lane) in flight
+      for (int r = warp; r < BM; r += 4 * MOVER_WARPS) {
+        for (int v0 = 0; v0 < vec_per_row; v0 += 32 * 4) {
+          uint4 a[4][4];
 #pragma unroll
-        for (int q = 0; q < UNR; q++) {
-          const int e = i + q * NUM_THREADS;
-          if (contig) {
-            a[q] = sp[e];
-          } else {
-            const int rr = e / vec_per_row;
-            a[q] = sp[(size_t)rr * src_row + (e - rr * vec_per_row)];
+          for (int q = 0; q < 4; q++) {
+            const int rr = r + q * MOVER_WARPS;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const int v = v0 + j * 32 + lane;
+              if (rr < BM && v < vec_per_row) a[q][j] = sp[(size_t)rr * src_row + v];
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            const int rr = r + q * MOVER_WARPS;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const int v = v0 + j * 32 + lane;
+              if (rr < BM && v < vec_per_row) dp[(size_t)rr * vec_per_row + v] = a[q][j];
+            }
           }
         }
-#pragma unroll
-        for (int q = 0; q < UNR; q++) dp[i + q * NUM_THREADS] = a[q];
       }
-      for (; i < unit_vecs; i += NUM_THREADS) {
-        const int rr = i / vec_per_row;
-        dp[i] = sp[(size_t)rr * src_row + (i - rr * vec_per_row)];
-      }
-    };
-    auto peer_pass = [&]() {
-      for (int j = 1; j < cp.n_ranks; j++)
-        for (int rb = b_lo + gidx; rb < b_hi; rb += gctas) copy_block((cp.rank + j) % cp.n_ranks, rb);
       __threadfence_system();
-      __syncthreads();
-      const int mine = (b_hi - b_lo - gidx + gctas - 1) / gctas;            // blocks of this CTA per peer
-      for (int k = threadIdx.x; k < mine * (cp.n_ranks - 1); k += NUM_THREADS) {
-        const int dst_rank = (cp.rank + 1 + k / mine) % cp.n_ranks;
-        const int rb = b_lo + gidx + (k % mine) * gctas;
-        red_release_sys_add(cp.ag_flags[dst_rank] + cp.rank * bpr + rb, (unsigned)MOVER_WARPS);
-      }
-    };
-    auto local_pass = [&]() {
-      for (int rb = b_lo + gidx; rb < b_hi; rb += gctas) copy_block(cp.rank, rb);
-    };
-    if (gidx < gctas) {
-      if (group == 0) { peer_pass(); local_pass(); }
-      else { local_pass(); peer_pass(); }
+      __syncwarp();
+      if (lane == 0) red_release_sys_add(cp.ag_flags[dst_rank] + cp.rank * cp.blocks_per_rank + rb, 1u);
     }
     return;
   }
@@ -385,9 +364,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       if (MODE == 2 && owner == cp.rank) {
         // Rows that this rank keeps (its tiles come last in the tile order, so the peers' partials of
-        // these rows, which they produce FIRST, have normally landed in the receive area long ago):
+        // these rows, which they produce FIRST, are on their way or already in the receive area):
         // wait for them, add them to the accumulator and store the finished bf16 rows.  No trip
-        // through the receive area for the own partial, no second kernel for the sum.
+        // through the receive area for the own partial, no second kernel for the sum.  (Parking the
+        // tiles whose partials are not in yet and summing them after the main loop was measured
+        // slower: the wait only moves to the end of the kernel, and the sum is then serial.)
         if (rs_npend > 0) {
           // the counts of the tiles already sent must leave before this rank starts waiting for its
           // peers: they are waiting for exactly those counts
