@@ -40,6 +40,13 @@ constexpr int MOE_MAX_TOPK = 8;
 constexpr int ROUTER_TOKENS = 32;       // tokens per router block (the unit of the within-block ranks)
 constexpr int ROUTER_THREADS = 256;
 
+// A copy routed to a row beyond the expert-side capacity is DROPPED (not dispatched, contributes
+// nothing to the combine), as in capacity-factor routing; it is counted, not treated as a failure:
+// word 2 = dropped copies / overfull plans since the last read, word 3 = largest row count asked for.
+__device__ __forceinline__ void moe_overflow(unsigned rows_wanted) {
+  atomicAdd(&g_moe_status[2], 1u);
+  atomicMax(&g_moe_status[3], rows_wanted);
+}
 __device__ __forceinline__ void moe_fail(unsigned code, unsigned where) {
   if (atomicCAS(&g_moe_status[0], 0u, code) == 0u) atomicExch(&g_moe_status[1], where);
 }
@@ -210,7 +217,7 @@ __global__ void __launch_bounds__(256) moe_plan_kernel(const PlanParams p) {
       if (le == p.LE - 1) {
         const int end = base + ((tot + 127) & ~127);
         p.seg[2 * p.LE] = end;
-        if (end > p.cap) moe_fail(3u, (unsigned)end);       // more rows routed here than the buffers hold
+        if (end > p.cap) moe_overflow((unsigned)end);        // more rows routed here than the buffers hold: the excess is dropped
       }
     }
   }
@@ -274,7 +281,7 @@ __global__ void __launch_bounds__(256) moe_push_kernel(const PushParams p) {
           row = p.rows[(size_t)t * p.k + s];
         }
         if (e_ok && row >= 0 && row < p.cap) drow[s] = reinterpret_cast<uint4*>(p.dst[e / p.LE] + (size_t)row * p.H);
-        else if (lane == 0) moe_fail(4u, (unsigned)row);
+        else if (lane == 0) { if (e_ok && row >= p.cap) moe_overflow((unsigned)row + 1u); else moe_fail(4u, (unsigned)row); }
         if (p.scale) sc[s] = p.scale[(size_t)t * p.k + s];
       }
     }
@@ -355,7 +362,7 @@ __global__ void __launch_bounds__(256) moe_pull_kernel(const PullParams p) {
         const int row = p.rows[(size_t)t * p.k + s];
         if (e >= 0 && e < p.E && row >= 0 && row < p.cap)
           srow[s] = reinterpret_cast<const uint4*>(p.src[e / p.LE] + (size_t)row * p.H);
-        else if (lane == 0) moe_fail(5u, (unsigned)row);
+        else if (lane == 0 && !(e >= 0 && e < p.E && row >= p.cap)) moe_fail(5u, (unsigned)row);   // beyond capacity: dropped at dispatch
         if (p.w) wt[s] = p.w[(size_t)t * p.k + s];
       }
     }

@@ -220,7 +220,22 @@ def device_status() -> dict:
         getattr(lib, sym)(ctypes.cast(buf, ctypes.c_void_p))
         if buf[0]:
             out[family] = (int(buf[0]), int(buf[1]))
+        if sym == "lb_moe_status" and buf[2]:
+            MOE_DROPPED["events"] += int(buf[2])
+            MOE_DROPPED["max_rows"] = max(MOE_DROPPED["max_rows"], int(buf[3]))
     return out
+
+
+# Copies of tokens that expert-parallel routing dropped because an expert's rows exceeded the capacity of
+# the exchange buffers (``model.moe_capacity_factor``): not an error, but worth a line in the log.
+MOE_DROPPED = {"events": 0, "max_rows": 0}
+
+
+def take_moe_dropped() -> dict:
+    """Counts gathered by the last ``device_status`` calls, reset on read."""
+    d = dict(MOE_DROPPED)
+    MOE_DROPPED["events"], MOE_DROPPED["max_rows"] = 0, 0
+    return d
 
 
 def raise_on_device_status() -> None:

@@ -16,8 +16,9 @@ and the mirror image in backward (``lb_moe_pull`` with dot products for the rout
 ``lb_moe_push`` of the scaled output gradient, ragged data / weight gradients, ``lb_moe_pull`` of the
 input gradient, ``lb_moe_router_bwd``).  Per-expert token counts exist only in device memory: the
 host never waits for them, every tensor on the expert side has the static capacity
-``ceil(capacity_factor * tokens * top_k)`` rows (+ padding), and a routing that would overflow it
-sets a status word (``native.raise_on_device_status``) instead of writing out of bounds.
+``ceil(capacity_factor * tokens * top_k)`` rows (+ padding), and the copies a routing sends beyond it
+are dropped (not dispatched, no contribution to the combine), counted in a status word that the
+trainer reports (``native.take_moe_dropped``).
 
 With one rank (no expert parallelism) the same kernels run on ordinary device tensors; with several,
 the exchange buffers and flag words live in ``torch.distributed._symmetric_memory``.
@@ -285,8 +286,8 @@ def fused_moe(x: torch.Tensor, gate_w: torch.Tensor, expert_ws: Sequence[torch.T
     T, H = x.shape
     n = dist.get_world_size(group) if group is not None else 1
     LE = num_experts // n
-    if n == 1:
-        cap = _up(T * topk, 128) + LE * 128
+    if n == 1 and capacity_factor >= 1.0:
+        cap = _up(T * topk, 128) + LE * 128          # one rank can never receive more than its own copies
     else:
         cap = _up(int(capacity_factor * T * topk), 128) + LE * 128
     ws = workspace(group, H, cap, num_experts, x.device)

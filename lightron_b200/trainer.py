@@ -219,6 +219,10 @@ class Trainer:
                 last_loss = float(loss)                            # the only host sync, once per log interval
                 if self.device.type == "cuda" and native.available():
                     native.raise_on_device_status()                # bounded waits that ran out inside a kernel
+                    dropped = native.take_moe_dropped()
+                    if dropped["events"]:
+                        print(f"[rank {ctx.rank}] step {self.step}: expert capacity exceeded, {dropped['events']} routed copies / plans "
+                              f"dropped (largest demand {dropped['max_rows']} rows; raise model.moe_capacity_factor)", flush=True)
                 self._check_liveness()
                 if is_log:
                     tps_wall = (self.tokens_seen - tokens0) / max(time.time() - start, 1e-9)

@@ -155,6 +155,34 @@ def test_fused_moe_matches_fp32_oracle():
         assert e_k < max(1.5 * e_lib, 2e-2), f"{name}: kernel chain {e_k:.4f} vs library path {e_lib:.4f}"
 
 
+def test_fused_moe_drops_copies_beyond_capacity():
+    """Expert-side buffers smaller than the routed load: the excess copies are dropped and counted, nothing is
+    written out of bounds, nothing raises, and forward / backward stay finite."""
+    from lightron_b200.models.moe import MoEFeedForward
+    from lightron_b200.ops import native
+    os.environ["LIGHTRON_FUSED_EP"] = "1"
+    try:
+        model, opt, args = _tiny_moe()
+        ff = next(b.feed_forward for b in model.layers.values() if isinstance(b.feed_forward, MoEFeedForward))
+        ff.capacity_factor = 0.4                          # 512 routed copies, room for ~205 (+ padding)
+        native.device_status(); native.take_moe_dropped()
+        x = _rand(256, args.dim, seed=3).requires_grad_(True)
+        opt.zero_grad()
+        y = ff(x)
+        (y.float().sum() + ff.last_aux_loss).backward()
+        torch.cuda.synchronize()
+        assert not native.device_status()                 # a drop is not a failure
+        dropped = native.take_moe_dropped()
+        assert dropped["events"] > 0 and dropped["max_rows"] > 0
+        assert torch.isfinite(y.float()).all() and torch.isfinite(x.grad.float()).all()
+        kept = (y.float().abs().sum(dim=1) > 0).float().mean().item()
+        assert 0.2 < kept <= 1.0                          # tokens whose copies were all dropped give zero rows
+        for p in ff.parameters():
+            assert torch.isfinite(p.grad.float()).all()
+    finally:
+        os.environ.pop("LIGHTRON_FUSED_EP", None)
+
+
 def test_fused_moe_model_step():
     """A whole small MoE model: the loss of the kernel-chain run agrees with the library-call run."""
     from lightron_b200.ops import native
