@@ -82,8 +82,11 @@ __device__ __forceinline__ float exp2_poly(float x) {
   p = fmaf(p, f, 1.0f);
   return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
+// Off by default: measured at B8 S2048 32q/4kv d64, every 2nd / 4th / 8th pair on the polynomial gave
+// 0.394 / 0.333 / 0.335 ms against 0.316 ms with the MUFU alone (the extra FMA-pipe instructions cost
+// more issue slots than the MUFU cycles they free).
 #ifndef LB_FA_POLY_EVERY
-#define LB_FA_POLY_EVERY 4
+#define LB_FA_POLY_EVERY 0
 #endif
 
 template <int D>

@@ -164,9 +164,9 @@ def test_fused_moe_drops_copies_beyond_capacity():
     try:
         model, opt, args = _tiny_moe()
         ff = next(b.feed_forward for b in model.layers.values() if isinstance(b.feed_forward, MoEFeedForward))
-        ff.capacity_factor = 0.4                          # 512 routed copies, room for ~205 (+ padding)
+        ff.capacity_factor = 0.25                         # 4096 routed copies, room for 1024 (+ 512 rows of padding)
         native.device_status(); native.take_moe_dropped()
-        x = _rand(256, args.dim, seed=3).requires_grad_(True)
+        x = _rand(2048, args.dim, seed=3).requires_grad_(True)
         opt.zero_grad()
         y = ff(x)
         (y.float().sum() + ff.last_aux_loss).backward()
@@ -176,7 +176,7 @@ def test_fused_moe_drops_copies_beyond_capacity():
         assert dropped["events"] > 0 and dropped["max_rows"] > 0
         assert torch.isfinite(y.float()).all() and torch.isfinite(x.grad.float()).all()
         kept = (y.float().abs().sum(dim=1) > 0).float().mean().item()
-        assert 0.2 < kept <= 1.0                          # tokens whose copies were all dropped give zero rows
+        assert 0.1 < kept < 1.0                           # tokens whose copies were all dropped give zero rows
         for p in ff.parameters():
             assert torch.isfinite(p.grad.float()).all()
     finally:
