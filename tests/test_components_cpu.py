@@ -81,6 +81,33 @@ def test_dataloader_shapes_targets_and_resume():
     assert torch.equal(next(dl2)["input_ids"], b1["input_ids"])
 
 
+def test_synthetic_samples_do_not_depend_on_the_batching():
+    """Sample i is a function of (seed, i): one micro-batch of 8 holds the rows of 8 micro-batches of 1, and of
+    the micro-batches two data-parallel ranks would draw."""
+    from lightron_b200.data import SyntheticTokens
+    ds = SyntheticTokens(1000, 32, seed=3)
+    whole = ds.batch(16, 8)
+    singles = torch.cat([ds.batch(16 + i, 1) for i in range(8)])
+    halves = torch.cat([ds.batch(16, 4), ds.batch(20, 4)])
+    assert torch.equal(whole, singles) and torch.equal(whole, halves)
+    assert not torch.equal(whole[0], whole[1])
+    assert not torch.equal(SyntheticTokens(1000, 32, seed=4).batch(16, 8), whole)
+
+
+def test_swiglu_mlp_fallback_matches_the_composed_ops():
+    """Off the GPU ``swiglu_mlp`` is the three composed ops (and the oracle formula)."""
+    from lightron_b200.ops import functional as OF
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(12, 16, generator=g, requires_grad=True)
+    w1, w3 = torch.randn(24, 16, generator=g) * 0.1, torch.randn(24, 16, generator=g) * 0.1
+    w2 = torch.randn(16, 24, generator=g) * 0.1
+    y = OF.swiglu_mlp(x, w1, w3, w2)
+    want = (torch.nn.functional.silu(x @ w1.t()) * (x @ w3.t())) @ w2.t()
+    assert torch.allclose(y, want, atol=1e-5)
+    y.sum().backward()
+    assert x.grad is not None and torch.isfinite(x.grad).all()
+
+
 def test_hf_key_mapping_roundtrip_and_rope_layout():
     from lightron_b200.models import LightronTransformer, init_weights
     from lightron_b200.utils import convert_hf_llama_state_dict, export_hf_llama_state_dict, load_hf_llama_weights
