@@ -1,10 +1,13 @@
 """Small, self-terminating workloads for profiling single kernels under ncu.
 
-    python -m lightron_b200.profile_kernels gemm|grouped|normbwd|attn|norm
+    python -m lightron_b200.profile_kernels gemm|grouped|normbwd|attn|norm|attn_full|mlp
 
 Each mode launches its kernel a few times on inputs larger than L2 but well under 1 GB, prints
 CUDA-event timings and exits; capture with e.g.
     ncu --set full --clock-control none -k regex:gemm_bf16 -s 2 -c 1 -o out python -m lightron_b200.profile_kernels gemm
+``attn_full`` (the attention kernels at the 1.1 B and 8 B layer shapes next to the PyTorch library
+attention) and ``mlp`` (the SwiGLU epilogues against GEMM + separate pass) are timing-only modes at full
+size: CUDA events, not meant for ncu.
 """
 from __future__ import annotations
 
@@ -80,8 +83,55 @@ def main(mode: str) -> None:
         ms = _time(lambda: torch.autograd.grad([h, y], [x, r, w], [dh, dyy], retain_graph=True), iters=3)
         gb = 4 * rows * cols * 2 / 1e9                 # dy, x, dres in; dx out (dx doubles as the residual gradient)
         print(f"add_rmsnorm bwd {rows}x{cols}: {ms:.3f} ms  {gb / ms * 1e3:.0f} GB/s (autograd call, both kernels)")
+    elif mode == "attn_full":
+        import torch.nn.functional as F
+        for (B, S, hq, hkv, d) in [(8, 2048, 32, 4, 64), (1, 8192, 32, 8, 128), (2, 4096, 16, 16, 64)]:
+            q = torch.randn(B, S, hq, d, device=dev, dtype=torch.bfloat16)
+            k = torch.randn(B, S, hkv, d, device=dev, dtype=torch.bfloat16)
+            v = torch.randn(B, S, hkv, d, device=dev, dtype=torch.bfloat16)
+            fl = 4.0 * B * hq * S * S * d / 2
+            sc = d ** -0.5
+            t_f = _time(lambda: OF.flash_fwd_native(q, k, v, True, sc), iters=10)
+            o, lse = OF.flash_fwd_native(q, k, v, True, sc)
+            do = torch.randn_like(o)
+            t_b = _time(lambda: OF.flash_bwd_native(q, k, v, o, lse, do, True, sc), iters=10)
+            # the library attention the reference calls (model/model.py:193-198), K / V expanded to the query heads
+            qt = q.transpose(1, 2)
+            kt, vt = (t.transpose(1, 2).repeat_interleave(hq // hkv, 1) for t in (k, v))
+            t_lib = _time(lambda: F.scaled_dot_product_attention(qt, kt, vt, is_causal=True), iters=10)
+            qr, kr, vr = (t.clone().requires_grad_(True) for t in (qt, kt, vt))
+
+            def lib_fb():
+                F.scaled_dot_product_attention(qr, kr, vr, is_causal=True).backward(do.transpose(1, 2))
+            t_lib_fb = _time(lib_fb, iters=10)
+            print(f"B{B} S{S} hq{hq} hkv{hkv} d{d}: fwd {t_f:.3f} ms {fl / t_f / 1e9:.0f} TFLOP/s | bwd {t_b:.3f} ms "
+                  f"{2.5 * fl / t_b / 1e9:.0f} TFLOP/s | library fwd {t_lib:.3f} ms {fl / t_lib / 1e9:.0f} TFLOP/s, "
+                  f"fwd+bwd {t_lib_fb:.3f} ms", flush=True)
+    elif mode == "mlp":
+        from .ops import native
+        T, K, I = 16384, 2048, 5632
+        x = torch.randn(T, K, device=dev, dtype=torch.bfloat16)
+        w13 = torch.randn(2 * I, K, device=dev, dtype=torch.bfloat16) * 0.02
+        w2 = torch.randn(K, I, device=dev, dtype=torch.bfloat16) * 0.02
+        dy = torch.randn(T, K, device=dev, dtype=torch.bfloat16)
+        gu = torch.empty(T, 2 * I, device=dev, dtype=torch.bfloat16)
+        h = torch.empty(T, I, device=dev, dtype=torch.bfloat16)
+        dgu, dh = torch.empty_like(gu), torch.empty_like(h)
+        dw2 = torch.zeros(K, I, device=dev, dtype=torch.bfloat16)
+        st = native.stream_ptr
+        t_g = _time(lambda: OF.gemm_grouped([(x, w13, False, False, gu, False)]), iters=10)
+        t_s = _time(lambda: native.call("lb_swiglu_fwd", gu.data_ptr(), h.data_ptr(), T, I, gu.stride(0), st()), iters=10)
+        t_e = _time(lambda: OF.gemm_grouped([(x, w13, False, False, gu, False, 1, h, I)]), iters=10)
+        print(f"gate | up GEMM {t_g:.3f} ms + SwiGLU pass {t_s:.3f} ms = {t_g + t_s:.3f} ms | with the epilogue {t_e:.3f} ms")
+        t_p = _time(lambda: OF.gemm_grouped([(dy, h, True, True, dw2, True), (dy, w2, False, True, dh, False)]), iters=10)
+        t_sb = _time(lambda: native.call("lb_swiglu_bwd", gu.data_ptr(), dh.data_ptr(), dgu.data_ptr(), T, I, gu.stride(0), st()),
+                     iters=10)
+        t_pe = _time(lambda: OF.gemm_grouped([(dy, h, True, True, dw2, True), (dy, w2, False, True, dgu, False, 2, gu, I)]),
+                     iters=10)
+        print(f"[weight + data gradient of down] {t_p:.3f} ms + SwiGLU-backward pass {t_sb:.3f} ms = {t_p + t_sb:.3f} ms | "
+              f"with the epilogue {t_pe:.3f} ms")
     else:
-        raise SystemExit("mode: gemm | grouped | normbwd | attn | norm")
+        raise SystemExit("mode: gemm | grouped | normbwd | attn | norm | attn_full | mlp")
 
 
 if __name__ == "__main__":
