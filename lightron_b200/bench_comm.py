@@ -23,6 +23,8 @@ import torch.distributed as dist
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=16384)
+    ap.add_argument("--publish", action="store_true",
+                    help="only measure what publishing an SM-issued peer copy costs (fence + flag per chunk) and exit")
     args = ap.parse_args()
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     from bench import ClockSampler
@@ -73,6 +75,29 @@ def main() -> None:
             t_sm, _ = bench(lambda: native.call("lb_peer_copy", src.data_ptr(), peer.data_ptr(), nbytes, mode, ctas,
                                                 native.stream_ptr()), iters=5)
             sm_rates.append((label, ctas, nbytes / t_sm / 1e6))
+    if args.publish:
+        # lb_peer_copy_flagged: the same copy, every chunk followed by a system-scope fence and a release-add on a
+        # flag word in the peer's memory (mode 2: the whole CTA; mode 3: a signalling warp), 64 MiB
+        nb = 64 << 20
+        fbuf = symm_mem.empty(1 << 20, dtype=torch.uint8, device=dev)
+        fbuf.zero_()
+        fh = symm_mem.rendezvous(fbuf, group=g)
+        pflags = fh.get_buffer((rank + 1) % world, (1 << 20,), torch.uint8)
+        lines = []
+        for ctas in (16, 32):
+            t, _ = bench(lambda: native.call("lb_peer_copy", src.data_ptr(), peer.data_ptr(), nb, 0, ctas, native.stream_ptr()))
+            lines.append(f"plain copy, {ctas} CTAs: {nb / t / 1e6:.0f} GB/s")
+            for mode in (2, 3):
+                for chunk in (128 << 10, 512 << 10, 2 << 20):
+                    t, _ = bench(lambda: native.call("lb_peer_copy_flagged", src.data_ptr(), peer.data_ptr(), nb, mode, ctas,
+                                                     chunk, pflags.data_ptr(), native.stream_ptr()))
+                    lines.append(f"mode {mode}, {ctas} CTAs, chunk {chunk >> 10} KiB: {nb / t / 1e6:.0f} GB/s")
+        native.raise_on_device_status()
+        if rank == 0:
+            print("\n".join(lines), flush=True)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     rows = []
     for name, N, K in [("qkv", 2560 // world, 2048), ("gate+up", 11264 // world, 2048), ("LM head", 32000 // world, 2048),
                        ("dgrad of down (dy gathered)", 5632 // world, 2048), ("dgrad of wo (dy gathered)", 2048 // world, 2048)]:
