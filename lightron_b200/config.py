@@ -160,6 +160,8 @@ class TrainingConfig:
     grad_clip: float = 0.0
     jsonl_log: Optional[str] = None
     heartbeat_timeout_s: float = 600.0   # a rank without a heartbeat for this long is reported (0 disables)
+    profile_steps: Optional[tuple] = None   # (first, last): torch.profiler trace of these steps on the log rank
+    profile_dir: str = "."               # where the chrome trace (lightron_trace_rank<r>.json) goes
 
 
 @dataclass

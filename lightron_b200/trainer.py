@@ -201,7 +201,16 @@ class Trainer:
         start = time.time()
         first_step, tokens0 = self.step, self.tokens_seen
         last_loss = float("nan")
+        prof = None
         while self.step < t.total_steps:
+            # optional torch.profiler window (training.profile_steps = [first, last], log rank only): the
+            # steps inside it run under the profiler and are not representative of the step time
+            if t.profile_steps and is_log and prof is None and self.step + 1 == int(t.profile_steps[0]):
+                acts = [torch.profiler.ProfilerActivity.CPU]
+                if self.device.type == "cuda":
+                    acts.append(torch.profiler.ProfilerActivity.CUDA)
+                prof = torch.profiler.profile(activities=acts)
+                prof.__enter__()
             self.timer.start()
             if self.device.type == "cuda":
                 torch.cuda.nvtx.range_push(f"step {self.step + 1}")
@@ -209,6 +218,12 @@ class Trainer:
             if self.device.type == "cuda":
                 torch.cuda.nvtx.range_pop()
             self.timer.stop()
+            if prof is not None and (self.step >= int(t.profile_steps[1]) or self.step == t.total_steps):
+                prof.__exit__(None, None, None)
+                trace = os.path.join(t.profile_dir, f"lightron_trace_rank{ctx.rank}.json")
+                prof.export_chrome_trace(trace)
+                print(f"profiler trace of steps {t.profile_steps[0]}-{self.step} written to {trace}", flush=True)
+                prof, t.profile_steps = None, None
             if self.step % t.log_interval == 0 or self.step == t.total_steps:
                 ms = self.timer.mean_ms_max_over_ranks()          # device time, MAX over ranks
                 # the reference prints rank 0's local loss (trainer.py:308-314); here it is the mean

@@ -172,3 +172,20 @@ def test_checkpoint_save_resume_and_corruption(tmp_path):
     with pytest.raises(RuntimeError, match="unreadable"):
         Trainer(parse_config(raw3, env={}))
     mesh.set_context(None)
+
+
+def test_profiler_window_writes_a_trace(tmp_path):
+    """``training.profile_steps`` runs the chosen steps under torch.profiler and leaves a chrome trace."""
+    import json
+    from lightron_b200.trainer import Trainer
+    mesh.set_context(None)
+    raw = copy.deepcopy(RAW)
+    raw["distributed"] = {}
+    raw["training"].update(total_steps=4, save_final=False, profile_steps=[2, 3], profile_dir=str(tmp_path))
+    out = Trainer(parse_config(raw, env={})).fit()
+    assert out["steps"] == 4
+    trace = tmp_path / "lightron_trace_rank0.json"
+    assert trace.exists()
+    events = json.loads(trace.read_text())["traceEvents"]
+    assert len(events) > 10
+    mesh.set_context(None)

@@ -151,3 +151,51 @@ def test_bucket_hook_counts_each_parameter_once_and_skips_pending_or_unsynced():
     assert b.pending == 0 and launched == [b]
     opt._reset_buckets()
     assert b.pending == b.n_params and not b.seen
+
+
+_SAN_SCRIPT = r'''
+import ctypes, random, sys
+lib = ctypes.CDLL(sys.argv[1])
+random.seed(0)
+# host-only entry points (no CUDA call): the static schedule of the grouped GEMM for many shape sets
+for trial in range(200):
+    n = random.randint(1, 8)
+    IA = ctypes.c_int * n
+    M = IA(*[random.choice([8, 128, 1000, 4096, 16384]) for _ in range(n)])
+    N = IA(*[random.choice([8, 264, 2048, 11264]) for _ in range(n)])
+    K = IA(*[random.choice([8, 200, 2048, 16384]) for _ in range(n)])
+    out = (ctypes.c_longlong * 3)()
+    rc = lib.lb_gemm_grouped_plan(n, M, N, K, random.choice([1, 7, 148]), out)
+    assert rc == 0 and out[0] > 0 and out[1] >= out[0] and out[2] >= 1, (rc, list(out))
+IA1 = ctypes.c_int * 1
+out = (ctypes.c_longlong * 3)()
+assert lib.lb_gemm_grouped_plan(0, IA1(8), IA1(8), IA1(8), 148, out) != 0
+assert lib.lb_gemm_grouped_plan(1, IA1(-5), IA1(8), IA1(8), 148, out) != 0
+lib.lb_set_flag_wait_ns.argtypes = [ctypes.c_ulonglong]
+assert lib.lb_set_flag_wait_ns(5_000_000) == 0
+assert lib.lb_gemm_grouped_cached() == 0
+print("SANITIZED_HOST_OK")
+'''
+
+
+def test_host_code_under_address_and_ub_sanitizers(tmp_path):
+    """The C++ host side of the library (argument checks, the grouped GEMM's schedule builder) built with
+    -fsanitize=address,undefined and driven without a GPU: any out-of-bounds access, use after free or
+    undefined arithmetic in it aborts the child process."""
+    import shutil
+    import subprocess
+    import sys
+    from lightron_b200.csrc import build as B
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    if not os.path.exists(nvcc) or shutil.which("gcc") is None:
+        pytest.skip("needs nvcc and gcc")
+    asan = subprocess.run(["gcc", "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip()
+    if not os.path.isabs(asan) or not os.path.exists(asan):
+        pytest.skip("libasan not installed")
+    lib = B.build_sanitized(str(tmp_path / "liblightron_b200_asan.so"))
+    script = tmp_path / "san.py"
+    script.write_text(_SAN_SCRIPT)
+    env = dict(os.environ, LD_PRELOAD=asan, ASAN_OPTIONS="detect_leaks=0:protect_shadow_gap=0:abort_on_error=1",
+               UBSAN_OPTIONS="halt_on_error=1:print_stacktrace=1")
+    r = subprocess.run([sys.executable, str(script), lib], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "SANITIZED_HOST_OK" in r.stdout, r.stdout[-1500:] + r.stderr[-3000:]
