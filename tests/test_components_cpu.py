@@ -189,3 +189,20 @@ def test_profiler_window_writes_a_trace(tmp_path):
     events = json.loads(trace.read_text())["traceEvents"]
     assert len(events) > 10
     mesh.set_context(None)
+
+
+def test_two_runs_with_one_seed_end_bitwise_equal():
+    """Repeated-run determinism of the whole loop (data order, init, optimizer) on the oracle ops."""
+    from lightron_b200.trainer import Trainer
+    finals = []
+    for _ in range(2):
+        mesh.set_context(None)
+        raw = copy.deepcopy(RAW)
+        raw["distributed"] = {}
+        raw["training"].update(total_steps=3, save_final=False)
+        tr = Trainer(parse_config(raw, env={}))
+        tr.fit()
+        finals.append({k: v.clone() for k, v in tr.model.state_dict().items()})
+    mesh.set_context(None)
+    for k in finals[0]:
+        assert torch.equal(finals[0][k], finals[1][k]), k
