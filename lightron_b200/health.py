@@ -8,7 +8,13 @@ The reference has only the 10-minute NCCL timeout (trainer.py:103) and shape ass
   between steps; ``dead_ranks()`` lists the ranks whose beat is older than a limit, so that the
   survivors learn of a lost rank on the host, before their next launch;
 * ``guarded`` runs a host function in a watchdog thread and raises ``RankFailure`` if it does not
-  return in time (a collective whose peer never joined).
+  return in time (a collective whose peer never joined);
+* ``announce_failure`` / ``failed_ranks``: a rank that leaves the training loop with an exception says
+  so in the store, and a rank whose own step then fails (its collective timed out, the connection
+  closed) reports THAT rank as the cause instead of its own secondary error;
+* ``maybe_inject_failure``: host-side fault injection for tests (``LIGHTRON_INJECT_FAILURE=rank:step``
+  makes that rank raise at the start of that step, between steps, with nothing in flight).
+Recovery is a relaunch with ``training.resume`` pointing at the last periodic checkpoint.
 Device-side waits are bounded inside the kernels and surface through ``lb_device_status`` /
 ``symm.check_status``.  Nothing here, and no test of it, faults or hangs a GPU.
 """
@@ -26,6 +32,41 @@ import torch.distributed as dist
 
 class RankFailure(RuntimeError):
     pass
+
+
+class InjectedFailure(RuntimeError):
+    """Raised by ``maybe_inject_failure`` (tests of the detection and recovery path)."""
+
+
+def maybe_inject_failure(step: int, rank: int) -> None:
+    import os
+    spec = os.environ.get("LIGHTRON_INJECT_FAILURE")
+    if not spec:
+        return
+    r, s = spec.split(":")
+    if int(r) == rank and int(s) == step:
+        raise InjectedFailure(f"injected failure on rank {rank} before step {step}")
+
+
+def announce_failure(store, rank: int, reason: str) -> None:
+    try:
+        store.set(f"failed/{rank}", f"{time.time():.3f}:{reason[:300]}")
+    except Exception:                       # the store itself may be gone: nothing more to do
+        pass
+
+
+def failed_ranks(store, world_size: int, exclude: Optional[int] = None) -> Dict[int, str]:
+    out: Dict[int, str] = {}
+    for r in range(world_size):
+        if r == exclude:
+            continue
+        try:
+            if hasattr(store, "check") and not store.check([f"failed/{r}"]):
+                continue
+            out[r] = store.get(f"failed/{r}").decode().split(":", 1)[1]
+        except Exception:
+            continue
+    return out
 
 
 def check_config_agreement(cfg_dict: Dict[str, Any], group=None) -> None:

@@ -190,6 +190,25 @@ class Trainer:
         return path
 
     def fit(self) -> Dict[str, Any]:
+        """The training loop.  A rank that leaves it with an exception announces that in the store; a rank
+        whose own step then fails names the rank that failed first as the cause."""
+        from . import health
+        hb = self.heartbeat
+        try:
+            return self._fit()
+        except health.RankFailure:
+            raise
+        except Exception as e:
+            if hb is not None:
+                first = health.failed_ranks(hb.store, hb.world, exclude=hb.rank)
+                if first:
+                    raise health.RankFailure(f"rank(s) {sorted(first)} failed first ({'; '.join(first.values())}); this rank's "
+                                             f"own error was {type(e).__name__}: {str(e)[:200]}") from e
+                health.announce_failure(hb.store, hb.rank, f"{type(e).__name__}: {e}")
+            raise
+
+    def _fit(self) -> Dict[str, Any]:
+        from . import health
         t, ctx = self.cfg.training, self.ctx
         is_log = ctx.rank == ctx.log_rank
         tokens_per_step = self.dataloader.global_batch_size * t.seq_length
@@ -211,6 +230,7 @@ class Trainer:
                     acts.append(torch.profiler.ProfilerActivity.CUDA)
                 prof = torch.profiler.profile(activities=acts)
                 prof.__enter__()
+            health.maybe_inject_failure(self.step + 1, ctx.rank)
             self.timer.start()
             if self.device.type == "cuda":
                 torch.cuda.nvtx.range_push(f"step {self.step + 1}")

@@ -233,3 +233,47 @@ def test_checkpoint_resumes_under_another_layout(tmp_path):
         assert step == 3 and cursor == 3          # cursor recomputed from the step count (2), then one more batch
         assert opt_steps == 1                       # moments restarted
         assert loss == loss and loss < 20.0
+
+
+def _recovery_worker(rank, world, tmp, phase):
+    """dp2 run of 4 steps with a checkpoint every 2.  'full': uninterrupted.  'crash': rank 1 raises before
+    step 3 (host-side injection, nothing in flight).  'resume': relaunch from the step-2 checkpoint."""
+    import copy
+    from lightron_b200 import health
+    from lightron_b200.config import parse_config
+    from lightron_b200.trainer import Trainer
+    raw = copy.deepcopy(_RESHARD)
+    raw["distributed"]["dp_size"] = 2
+    raw["training"].update(total_steps=4, save_interval=2, save_final=False, log_interval=1, heartbeat_timeout_s=60.0,
+                           save_dir=os.path.join(tmp, "full" if phase == "full" else "crash"))
+    os.makedirs(raw["training"]["save_dir"], exist_ok=True)
+    os.environ.pop("LIGHTRON_INJECT_FAILURE", None)
+    if phase == "crash":
+        os.environ["LIGHTRON_INJECT_FAILURE"] = "1:3"
+    if phase == "resume":
+        raw["training"]["resume"] = os.path.join(tmp, "crash", "ckpt_step_2_tpsize_1_dpsize_2")
+    tr = Trainer(parse_config(raw, env={}))
+    try:
+        tr.fit()
+    except health.InjectedFailure as e:
+        return "injected", str(e), tr.step
+    except health.RankFailure as e:
+        return "rank_failure", str(e), tr.step
+    return "done", {k: v.float().numpy() for k, v in tr.model.state_dict().items()}, tr.step
+
+
+def test_injected_rank_failure_is_reported_and_recovered_from_the_last_checkpoint(tmp_path):
+    """A rank dies between steps (host-side injection): the survivor's collective times out, the survivor names
+    the rank that failed first, and a relaunch from the last periodic checkpoint ends with the weights of the
+    uninterrupted run."""
+    import numpy as np
+    full = run_distributed(_recovery_worker, 2, str(tmp_path), "full")
+    assert full[0][0] == "done" and full[0][2] == 4
+    crash = run_distributed(_recovery_worker, 2, str(tmp_path), "crash", pg_timeout_s=8)
+    assert crash[1][0] == "injected" and crash[1][2] == 2
+    assert crash[0][0] == "rank_failure" and "rank(s) [1] failed first" in crash[0][1] and "InjectedFailure" in crash[0][1]
+    assert os.path.exists(tmp_path / "crash" / "ckpt_step_2_tpsize_1_dpsize_2")
+    resumed = run_distributed(_recovery_worker, 2, str(tmp_path), "resume")
+    assert resumed[0][0] == "done" and resumed[0][2] == 4
+    for k, v in full[0][1].items():
+        assert np.allclose(v, resumed[0][1][k], atol=1e-6), k
