@@ -341,7 +341,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int it = 0;
     constexpr int RS_MAX_PEND = 24;
     unsigned int* rs_pend[RS_MAX_PEND];     // MODE 2: counters of tiles whose stores are not yet fenced
-    int rs_npend = 0;
+    int rs_npend = 0, rs_pend_owner = -1;
     for (int t = cta; t < p.num_tiles && ok; t += n_cta, it++) {
       const int acc = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
@@ -472,15 +472,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // Counting a tile needs a system-scope fence after its stores, and on NVLink that fence does
         // not return before everything this SM has stored to the peer has drained (tens of
         // microseconds).  The tiles that travel come first in the tile order, so their counts are
-        // kept and sent together: one fence when this CTA turns to the rows it keeps (or ends, or
-        // the list is full).
-        if (rs_npend == RS_MAX_PEND) {
+        // kept and sent together: one fence when the destination rank changes (tiles are ordered by
+        // destination, so with two ranks that is when this CTA turns to the rows it keeps), when the
+        // CTA ends, or when the list is full.
+        if (rs_npend > 0 && (owner != rs_pend_owner || rs_npend == RS_MAX_PEND)) {
           __threadfence_system();
           __syncwarp();
           if (lane == 0)
             for (int i = 0; i < rs_npend; i++) red_release_sys_add(rs_pend[i], 1u);
           rs_npend = 0;
         }
+        rs_pend_owner = owner;
         rs_pend[rs_npend++] = cp.rs_flags[owner] + cp.rank * cp.blocks_per_rank + lb;
         const int nvec = min(BN, p.N - n0) / 8;            // 16-byte vectors per row (<= 32)
         bf16* dst0 = cp.recv[owner] + ((size_t)cp.rank * cp.rows_per_rank + (size_t)lb * BM + quad * 32) * p.N + n0;
