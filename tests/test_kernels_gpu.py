@@ -252,6 +252,33 @@ def test_peer_copy_kernel_local(mode, nbytes, ctas):
     assert not native.device_status()
 
 
+def test_grouped_gemm_schedule_cache_stays_bounded():
+    """Callers whose shapes change from call to call must not grow the schedule cache (or device memory)
+    without bound: sweeps over 150 different row counts leave at most the cache's capacity of entries behind,
+    and a second sweep (every entry evicted and rebuilt) does not cost device memory."""
+    from lightron_b200.ops import functional as OF, native
+    lib = native.require()
+    a = _rand(1208, 64, seed=1)
+    b = _rand(64, 64, seed=2)
+    out = torch.empty(1208, 64, device="cuda", dtype=torch.bfloat16)
+
+    def sweep(check):
+        for i, M in enumerate(range(8, 1208, 8)):                  # 150 shape sets
+            OF.gemm_grouped([(a[:M], b, False, False, out[:M], False)])
+            if check and i % 37 == 0:
+                want = a[:M].float() @ b.float().t()
+                assert _rel_err(out[:M], want) < 1e-2, M
+        torch.cuda.synchronize()
+
+    sweep(True)                                                    # also pays every one-time allocation (library handles, ...)
+    assert lib.lb_gemm_grouped_cached() <= 128
+    free1 = torch.cuda.mem_get_info()[0]
+    sweep(False)
+    assert lib.lb_gemm_grouped_cached() <= 128
+    assert free1 - torch.cuda.mem_get_info()[0] < (8 << 20)
+    assert _gemm_status()[0] == 0
+
+
 def test_embedding_fwd_bwd_vocab_parallel():
     from lightron_b200.ops import functional as OF
     V, H, T = 1000, 256, 4096
